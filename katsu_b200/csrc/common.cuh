@@ -1,0 +1,120 @@
+// Shared internals of libkatsu_cuda.so: the context object, error plumbing and
+// small device helpers.  Nothing here is part of the C ABI (include/katsu_cuda.h).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "katsu_cuda.h"
+
+#define KATSU_NUM_SMS_B200 148
+
+struct katsu_cuda_ctx {
+    int device;
+    int num_sms;
+    int precision;
+    cudaStream_t stream;
+    uint64_t launches;
+    // Scratch in global memory for per-block partial results (dW partials,
+    // sum partials, split-K slabs).  Grown on demand, never shrunk, freed at
+    // shutdown.  Only the context's stream touches it, so launches that use
+    // it are serialised by stream order.
+    float *scratch;
+    size_t scratch_floats;
+    // Buffer written by katsu_cuda_flush_l2.
+    float *flush;
+    size_t flush_floats;
+    // Device status word for bounded waits (0 = ok).
+    int *status;
+    // NCCL communicator (void* so this header does not need nccl.h).
+    void *comm;
+    int comm_ranks;
+    int comm_rank;
+};
+
+struct katsu_cuda_event {
+    cudaEvent_t ev;
+};
+
+// Records a message for katsu_cuda_last_error_string and returns `code`.
+int32_t katsu_set_error(int32_t code, const char *fmt, ...);
+
+// Makes the context's device current; returns a status.
+int32_t katsu_bind(katsu_cuda_ctx *ctx);
+
+// Ensures ctx->scratch holds at least `floats` floats.
+int32_t katsu_scratch(katsu_cuda_ctx *ctx, size_t floats, float **out);
+
+#define KATSU_CUDA_TRY(expr)                                                              \
+    do {                                                                                  \
+        cudaError_t err__ = (expr);                                                       \
+        if (err__ != cudaSuccess)                                                         \
+            return katsu_set_error(err__ == cudaErrorMemoryAllocation ? KATSU_ERR_ALLOC   \
+                                                                      : KATSU_ERR_CUDA,   \
+                                   "%s failed: %s (%s:%d)", #expr,                        \
+                                   cudaGetErrorString(err__), __FILE__, __LINE__);        \
+    } while (0)
+
+#define KATSU_TRY(expr)                   \
+    do {                                  \
+        int32_t rc__ = (expr);            \
+        if (rc__ != KATSU_OK) return rc__; \
+    } while (0)
+
+#define KATSU_REQUIRE(cond, msg)                                          \
+    do {                                                                  \
+        if (!(cond)) return katsu_set_error(KATSU_ERR_INVALID_ARG, "%s", msg); \
+    } while (0)
+
+// After a <<<>>> launch: count it and surface launch-configuration errors.
+#define KATSU_LAUNCHED(ctx)                                                        \
+    do {                                                                           \
+        (ctx)->launches += 1;                                                      \
+        cudaError_t err__ = cudaGetLastError();                                    \
+        if (err__ != cudaSuccess)                                                  \
+            return katsu_set_error(KATSU_ERR_CUDA, "kernel launch failed: %s (%s:%d)", \
+                                   cudaGetErrorString(err__), __FILE__, __LINE__); \
+    } while (0)
+
+// Launches `kernel` (a __global__ function or a pointer to one) on the
+// context's stream, counts it and reports launch-configuration errors.
+#ifndef KATSU_LAUNCH
+#define KATSU_LAUNCH(ctx, kernel, grid, block, smem, ...)                   \
+    do {                                                                    \
+        kernel<<<(grid), (block), (smem), (ctx)->stream>>>(__VA_ARGS__);    \
+        KATSU_LAUNCHED(ctx);                                                \
+    } while (0)
+#endif
+
+// Start of the block's dynamic shared memory.
+#ifndef KATSU_DYNAMIC_SMEM_DEFINED
+__device__ __forceinline__ float *katsu_dynamic_smem() {
+    extern __shared__ __align__(128) unsigned char katsu_smem_raw[];
+    return reinterpret_cast<float *>(katsu_smem_raw);
+}
+#endif
+
+static inline size_t katsu_div_up(size_t a, size_t b) { return (a + b - 1) / b; }
+
+// Internal entry points shared between translation units.
+int32_t katsu_conv_direct_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,
+                              size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                              size_t stride, size_t pad, size_t oh, size_t ow);
+int32_t katsu_conv_direct_dx(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx,
+                             size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                             size_t stride, size_t pad, size_t oh, size_t ow, int accumulate);
+int32_t katsu_conv_direct_dw(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw,
+                             size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                             size_t stride, size_t pad, size_t oh, size_t ow, int accumulate);
+
+// Low-channel 3x3 stride-1 pad-1 stencil path; *handled = 0 when the shape is
+// not one it covers (the caller then uses another kernel).
+int32_t katsu_conv_stencil_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,
+                               size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                               size_t stride, size_t pad, int *handled);
+int32_t katsu_conv_stencil_bwd(katsu_cuda_ctx *ctx, const float *x, const float *w, const float *g,
+                               float *dx, float *dw,
+                               size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                               size_t stride, size_t pad, int accumulate, int *handled);

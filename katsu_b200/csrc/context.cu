@@ -1,0 +1,280 @@
+// Context, memory, transfer and timing entry points of the C ABI.
+#include <stdarg.h>
+#include <string.h>
+
+#include <new>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+
+int32_t katsu_set_error(int32_t code, const char *fmt, ...) {
+    va_list args;
+    va_start(args, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, args);
+    va_end(args);
+    return code;
+}
+
+extern "C" const char *katsu_cuda_last_error_string(void) { return g_error; }
+
+int32_t katsu_bind(katsu_cuda_ctx *ctx) {
+    if (ctx == nullptr) return katsu_set_error(KATSU_ERR_INVALID_ARG, "null context");
+    KATSU_CUDA_TRY(cudaSetDevice(ctx->device));
+    return KATSU_OK;
+}
+
+int32_t katsu_scratch(katsu_cuda_ctx *ctx, size_t floats, float **out) {
+    if (floats > ctx->scratch_floats) {
+        // Earlier launches may still be reading the old block.
+        KATSU_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+        if (ctx->scratch) KATSU_CUDA_TRY(cudaFree(ctx->scratch));
+        ctx->scratch = nullptr;
+        ctx->scratch_floats = 0;
+        size_t want = floats < (size_t(1) << 20) ? (size_t(1) << 20) : floats;
+        KATSU_CUDA_TRY(cudaMalloc(&ctx->scratch, want * sizeof(float)));
+        ctx->scratch_floats = want;
+    }
+    *out = ctx->scratch;
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_device_count(int32_t *out_count) {
+    KATSU_REQUIRE(out_count != nullptr, "out_count is null");
+    int n = 0;
+    cudaError_t err = cudaGetDeviceCount(&n);
+    if (err != cudaSuccess) {
+        *out_count = 0;
+        return katsu_set_error(KATSU_ERR_NO_DEVICE, "cudaGetDeviceCount: %s", cudaGetErrorString(err));
+    }
+    *out_count = n;
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_init(int32_t device, katsu_cuda_ctx **out_ctx) {
+    KATSU_REQUIRE(out_ctx != nullptr, "out_ctx is null");
+    *out_ctx = nullptr;
+    int n = 0;
+    cudaError_t err = cudaGetDeviceCount(&n);
+    if (err != cudaSuccess || n == 0)
+        return katsu_set_error(KATSU_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(err));
+    if (device < 0 || device >= n)
+        return katsu_set_error(KATSU_ERR_NO_DEVICE, "device ordinal %d out of range (0..%d)", device, n - 1);
+    KATSU_CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    KATSU_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return katsu_set_error(KATSU_ERR_NO_DEVICE,
+                               "device %d is sm_%d%d; this library only carries sm_100a code", device,
+                               prop.major, prop.minor);
+    katsu_cuda_ctx *ctx = new (std::nothrow) katsu_cuda_ctx();
+    if (ctx == nullptr) return katsu_set_error(KATSU_ERR_ALLOC, "out of host memory");
+    memset(ctx, 0, sizeof(*ctx));
+    ctx->device = device;
+    ctx->num_sms = prop.multiProcessorCount;
+    ctx->precision = KATSU_MODE_3XTF32;
+    err = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (err == cudaSuccess) err = cudaMalloc(&ctx->status, sizeof(int));
+    if (err == cudaSuccess) err = cudaMemsetAsync(ctx->status, 0, sizeof(int), ctx->stream);
+    if (err != cudaSuccess) {
+        if (ctx->stream) cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        return katsu_set_error(KATSU_ERR_CUDA, "context setup: %s", cudaGetErrorString(err));
+    }
+    *out_ctx = ctx;
+    return KATSU_OK;
+}
+
+int32_t katsu_comm_destroy_impl(katsu_cuda_ctx *ctx);
+
+extern "C" int32_t katsu_cuda_shutdown(katsu_cuda_ctx *ctx) {
+    KATSU_TRY(katsu_bind(ctx));
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->comm) katsu_comm_destroy_impl(ctx);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->flush) cudaFree(ctx->flush);
+    if (ctx->status) cudaFree(ctx->status);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_set_precision(katsu_cuda_ctx *ctx, int32_t mode) {
+    KATSU_REQUIRE(ctx != nullptr, "null context");
+    KATSU_REQUIRE(mode == KATSU_MODE_3XTF32 || mode == KATSU_MODE_TF32 || mode == KATSU_MODE_FP32,
+                  "unknown precision mode");
+    ctx->precision = mode;
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_get_precision(katsu_cuda_ctx *ctx, int32_t *out_mode) {
+    KATSU_REQUIRE(ctx != nullptr && out_mode != nullptr, "null argument");
+    *out_mode = ctx->precision;
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_launch_count(katsu_cuda_ctx *ctx, uint64_t *out_count) {
+    KATSU_REQUIRE(ctx != nullptr && out_count != nullptr, "null argument");
+    *out_count = ctx->launches;
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_stream(katsu_cuda_ctx *ctx, void **out_stream) {
+    KATSU_REQUIRE(ctx != nullptr && out_stream != nullptr, "null argument");
+    *out_stream = (void *)ctx->stream;
+    return KATSU_OK;
+}
+
+// ---- memory ----------------------------------------------------------------
+extern "C" int32_t katsu_cuda_alloc(katsu_cuda_ctx *ctx, size_t count, float **out_ptr) {
+    KATSU_REQUIRE(out_ptr != nullptr, "out_ptr is null");
+    *out_ptr = nullptr;
+    KATSU_TRY(katsu_bind(ctx));
+    if (count == 0) return KATSU_OK;
+    if (count > SIZE_MAX / sizeof(float))
+        return katsu_set_error(KATSU_ERR_ALLOC, "allocation of %zu floats overflows", count);
+    float *p = nullptr;
+    cudaError_t err = cudaMalloc(&p, count * sizeof(float));
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return katsu_set_error(KATSU_ERR_ALLOC, "cudaMalloc(%zu bytes): %s", count * sizeof(float),
+                               cudaGetErrorString(err));
+    }
+    err = cudaMemsetAsync(p, 0, count * sizeof(float), ctx->stream);
+    if (err != cudaSuccess) {
+        cudaFree(p);
+        return katsu_set_error(KATSU_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(err));
+    }
+    *out_ptr = p;
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_free(katsu_cuda_ctx *ctx, float *ptr) {
+    KATSU_TRY(katsu_bind(ctx));
+    if (ptr == nullptr) return KATSU_OK;
+    // cudaFree waits for work that may still use the block.
+    KATSU_CUDA_TRY(cudaFree(ptr));
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_zero(katsu_cuda_ctx *ctx, float *dst, size_t count) {
+    KATSU_TRY(katsu_bind(ctx));
+    if (count == 0) return KATSU_OK;
+    KATSU_REQUIRE(dst != nullptr, "dst is null");
+    KATSU_CUDA_TRY(cudaMemsetAsync(dst, 0, count * sizeof(float), ctx->stream));
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_h2d(katsu_cuda_ctx *ctx, float *dst_device, const float *src_host, size_t count) {
+    KATSU_TRY(katsu_bind(ctx));
+    if (count == 0) return KATSU_OK;
+    KATSU_REQUIRE(dst_device != nullptr && src_host != nullptr, "null buffer");
+    KATSU_CUDA_TRY(cudaMemcpyAsync(dst_device, src_host, count * sizeof(float), cudaMemcpyHostToDevice,
+                                   ctx->stream));
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_d2h(katsu_cuda_ctx *ctx, float *dst_host, const float *src_device, size_t count) {
+    KATSU_TRY(katsu_bind(ctx));
+    if (count != 0) {
+        KATSU_REQUIRE(dst_host != nullptr && src_device != nullptr, "null buffer");
+        KATSU_CUDA_TRY(cudaMemcpyAsync(dst_host, src_device, count * sizeof(float), cudaMemcpyDeviceToHost,
+                                       ctx->stream));
+    }
+    KATSU_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_d2d(katsu_cuda_ctx *ctx, float *dst_device, const float *src_device, size_t count) {
+    KATSU_TRY(katsu_bind(ctx));
+    if (count == 0) return KATSU_OK;
+    KATSU_REQUIRE(dst_device != nullptr && src_device != nullptr, "null buffer");
+    KATSU_CUDA_TRY(cudaMemcpyAsync(dst_device, src_device, count * sizeof(float), cudaMemcpyDeviceToDevice,
+                                   ctx->stream));
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_host_alloc(katsu_cuda_ctx *ctx, size_t count, float **out_ptr) {
+    KATSU_REQUIRE(out_ptr != nullptr, "out_ptr is null");
+    *out_ptr = nullptr;
+    KATSU_TRY(katsu_bind(ctx));
+    if (count == 0) return KATSU_OK;
+    void *p = nullptr;
+    cudaError_t err = cudaHostAlloc(&p, count * sizeof(float), cudaHostAllocDefault);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return katsu_set_error(KATSU_ERR_ALLOC, "cudaHostAlloc(%zu bytes): %s", count * sizeof(float),
+                               cudaGetErrorString(err));
+    }
+    *out_ptr = (float *)p;
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_host_free(katsu_cuda_ctx *ctx, float *ptr) {
+    KATSU_TRY(katsu_bind(ctx));
+    if (ptr == nullptr) return KATSU_OK;
+    KATSU_CUDA_TRY(cudaFreeHost(ptr));
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_sync(katsu_cuda_ctx *ctx) {
+    KATSU_TRY(katsu_bind(ctx));
+    KATSU_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    int status = 0;
+    KATSU_CUDA_TRY(cudaMemcpy(&status, ctx->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (status != 0) {
+        cudaMemset(ctx->status, 0, sizeof(int));
+        return katsu_set_error(KATSU_ERR_TIMEOUT, "a device-side wait gave up (status word %d)", status);
+    }
+    return KATSU_OK;
+}
+
+// ---- timing ----------------------------------------------------------------
+extern "C" int32_t katsu_cuda_event_create(katsu_cuda_ctx *ctx, katsu_cuda_event **out_event) {
+    KATSU_REQUIRE(out_event != nullptr, "out_event is null");
+    KATSU_TRY(katsu_bind(ctx));
+    katsu_cuda_event *e = new (std::nothrow) katsu_cuda_event();
+    if (e == nullptr) return katsu_set_error(KATSU_ERR_ALLOC, "out of host memory");
+    cudaError_t err = cudaEventCreate(&e->ev);
+    if (err != cudaSuccess) {
+        delete e;
+        return katsu_set_error(KATSU_ERR_CUDA, "cudaEventCreate: %s", cudaGetErrorString(err));
+    }
+    *out_event = e;
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_event_record(katsu_cuda_ctx *ctx, katsu_cuda_event *event) {
+    KATSU_REQUIRE(event != nullptr, "event is null");
+    KATSU_TRY(katsu_bind(ctx));
+    KATSU_CUDA_TRY(cudaEventRecord(event->ev, ctx->stream));
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_event_elapsed_ms(katsu_cuda_ctx *ctx, katsu_cuda_event *start,
+                                               katsu_cuda_event *stop, float *out_ms) {
+    KATSU_REQUIRE(start != nullptr && stop != nullptr && out_ms != nullptr, "null argument");
+    KATSU_TRY(katsu_bind(ctx));
+    KATSU_CUDA_TRY(cudaEventSynchronize(stop->ev));
+    KATSU_CUDA_TRY(cudaEventElapsedTime(out_ms, start->ev, stop->ev));
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_event_destroy(katsu_cuda_ctx *ctx, katsu_cuda_event *event) {
+    KATSU_TRY(katsu_bind(ctx));
+    if (event == nullptr) return KATSU_OK;
+    cudaEventDestroy(event->ev);
+    delete event;
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_flush_l2(katsu_cuda_ctx *ctx) {
+    KATSU_TRY(katsu_bind(ctx));
+    const size_t floats = size_t(64) << 20;  // 256 MiB, twice the 126 MB L2
+    if (ctx->flush == nullptr) {
+        KATSU_CUDA_TRY(cudaMalloc(&ctx->flush, floats * sizeof(float)));
+        ctx->flush_floats = floats;
+    }
+    KATSU_CUDA_TRY(cudaMemsetAsync(ctx->flush, 0, ctx->flush_floats * sizeof(float), ctx->stream));
+    return KATSU_OK;
+}

@@ -1,0 +1,70 @@
+// Conv2D entry points of the C ABI: argument checks, output geometry and the
+// choice of kernel family.  The arithmetic lives in conv_stencil.cu (low
+// channel counts) and conv_direct.cu (everything else on CUDA cores).
+#include "common.cuh"
+
+namespace {
+
+struct Geometry {
+    size_t oh, ow;
+};
+
+// Same output-size rule as Geometry::new, crates/katsu-core/src/conv2d.rs:197-210.
+// The caller has normally validated already; this guards the kernels.
+int32_t geometry(size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s, size_t stride, size_t pad,
+                 Geometry *g) {
+    if (c == 0 || k == 0 || r == 0 || s == 0)
+        return katsu_set_error(KATSU_ERR_INVALID_ARG, "weights must have positive OIHW dimensions");
+    if (stride == 0) return katsu_set_error(KATSU_ERR_INVALID_ARG, "stride must be positive");
+    if (h == 0 || wd == 0) return katsu_set_error(KATSU_ERR_INVALID_ARG, "H and W must be positive");
+    if (pad > (SIZE_MAX >> 2)) return katsu_set_error(KATSU_ERR_INVALID_ARG, "padding too large");
+    if (h + 2 * pad < r || wd + 2 * pad < s)
+        return katsu_set_error(KATSU_ERR_INVALID_ARG, "kernel exceeds padded input");
+    g->oh = (h + 2 * pad - r) / stride + 1;
+    g->ow = (wd + 2 * pad - s) / stride + 1;
+    return KATSU_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t katsu_cuda_conv2d_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,
+                                         size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                                         size_t stride, size_t pad) {
+    KATSU_TRY(katsu_bind(ctx));
+    Geometry g;
+    KATSU_TRY(geometry(c, h, wd, k, r, s, stride, pad, &g));
+    if (n == 0) return KATSU_OK;  // empty batch: y has no elements (conv2d.rs:195-196)
+    KATSU_REQUIRE(x != nullptr && w != nullptr && y != nullptr, "null tensor");
+    int handled = 0;
+    KATSU_TRY(katsu_conv_stencil_fwd(ctx, x, w, y, n, c, h, wd, k, r, s, stride, pad, &handled));
+    if (handled) return KATSU_OK;
+    return katsu_conv_direct_fwd(ctx, x, w, y, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow);
+}
+
+extern "C" int32_t katsu_cuda_conv2d_bwd(katsu_cuda_ctx *ctx, const float *x, const float *w, const float *gr,
+                                         float *dx, float *dw,
+                                         size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                                         size_t stride, size_t pad, int32_t accumulate) {
+    KATSU_TRY(katsu_bind(ctx));
+    Geometry g;
+    KATSU_TRY(geometry(c, h, wd, k, r, s, stride, pad, &g));
+    KATSU_REQUIRE(dx == nullptr || (const float *)dx != (const float *)dw, "dx and dw must not alias");
+    if (n == 0) {
+        // dx is empty; dw is a sum over no terms (conv2d.rs:283-284 leaves zeros).
+        if (dw != nullptr && !accumulate)
+            KATSU_CUDA_TRY(cudaMemsetAsync(dw, 0, k * c * r * s * sizeof(float), ctx->stream));
+        return KATSU_OK;
+    }
+    KATSU_REQUIRE(gr != nullptr, "null upstream gradient");
+    KATSU_REQUIRE(dx == nullptr || w != nullptr, "dx needs the weights");
+    KATSU_REQUIRE(dw == nullptr || x != nullptr, "dw needs the input");
+    int handled = 0;
+    KATSU_TRY(katsu_conv_stencil_bwd(ctx, x, w, gr, dx, dw, n, c, h, wd, k, r, s, stride, pad, accumulate,
+                                     &handled));
+    if (handled) return KATSU_OK;
+    if (dx != nullptr)
+        KATSU_TRY(katsu_conv_direct_dx(ctx, w, gr, dx, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow, accumulate));
+    if (dw != nullptr)
+        KATSU_TRY(katsu_conv_direct_dw(ctx, x, gr, dw, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow, accumulate));
+    return KATSU_OK;
+}
