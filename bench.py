@@ -1,0 +1,356 @@
+#!/usr/bin/env python3
+"""Benchmark of the Conv2D hot path: forward + dX + dW, images/s.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W]            this library on N B200s
+  python bench.py --impl reference [--gpus N] [--steps K] ...    the reference's CPU algorithm on the host cores
+
+Workload (default): the batched low-channel stem, x [256,3,224,224] ~U(-1,1),
+w [64,3,3,3] ~N(0, 2/27), stride 1, padding 1; upstream gradient g = 2y (the
+VJP seed of loss = sum(y*y)).  One step = conv2d_fwd, conv2d_bwd(dX),
+conv2d_bwd(dW) through the C ABI (+ one NCCL all-reduce of dW when N > 1, the
+batch being sharded over the ranks).  Inputs are synthetic and seeded
+(katsu_b200/workloads.py); y and g are larger than L2, so every step streams
+from HBM.
+
+One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from katsu_b200 import workloads  # noqa: E402
+
+METRIC = "conv2d_fwd_dx_dw_images_per_s"
+UNIT = "images/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            peaks = json.load(fh)
+        return float(peaks["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, sm_max, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                sm_max.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[3:7]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(sm_max), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def dist_env():
+    return (int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")),
+            int(os.environ.get("WORLD_SIZE", "1")))
+
+
+# ---------------------------------------------------------------------------
+# CPU legs (the only place this file touches oracle/)
+# ---------------------------------------------------------------------------
+def cpu_step(ref, x, w, spec, threaded: bool):
+    """One pass of the reference algorithm: forward, g = 2y, backward_buffers."""
+    y = ref.conv2d_forward(x, w, spec.x_shape, spec.w_shape, spec.stride, spec.pad, mt=threaded)
+    g = y + y
+    dx, dw = ref.conv2d_backward(x, w, g, spec.x_shape, spec.w_shape, spec.stride, spec.pad, mt=threaded)
+    return dx, dw
+
+
+def cpu_baseline(spec, sample_images: int):
+    """Single-threaded port of the reference on a bounded sample of the workload."""
+    from oracle import katsu_ref as ref
+
+    sample = spec.with_batch(sample_images)
+    x, w = workloads.conv_inputs(sample)
+    ref.lib().ko_set_num_threads(1)
+    t0 = time.perf_counter()
+    cpu_step(ref, x, w, sample, threaded=False)
+    dt = time.perf_counter() - t0
+    return {"value": sample_images / dt, "unit": UNIT, "cores": 1, "kind": "port",
+            "sample": f"{sample_images} of {spec.n} images of {spec.name}, one pass, {dt:.1f} s",
+            "host_cores_total": os.cpu_count()}
+
+
+def run_reference(args):
+    """The reference's CPU algorithm (oracle port; the Rust original has no toolchain here)
+    on all host threads, on a bounded sample of the same workload."""
+    rank, _, world = dist_env()
+    if rank != 0:
+        return 0
+    from oracle import katsu_ref as ref
+
+    spec = workloads.CONV[args.workload]
+    if args.batch:
+        spec = spec.with_batch(args.batch)
+    threads = os.cpu_count() or 1
+    ref.lib().ko_set_num_threads(threads)
+    sample_images = max(1, min(spec.n, threads))
+    sample = spec.with_batch(sample_images)
+    x, w = workloads.conv_inputs(sample)
+    for _ in range(args.warmup):
+        cpu_step(ref, x, w, sample, threaded=True)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(ref, x, w, sample, threaded=True)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = sample_images / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": spec.name, "x": spec.x_shape, "w": spec.w_shape, "stride": spec.stride,
+                   "padding": spec.pad, "global_batch": spec.n},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{sample_images} of {spec.n} images per step, OpenMP over images/channels"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def run_ours(args):
+    rank, local_rank, world = dist_env()
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    from katsu_b200 import cabi, dp
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
+
+    spec_full = workloads.CONV[args.workload]
+    if args.batch:
+        spec_full = spec_full.with_batch(args.batch)
+    if args.scaling == "strong":
+        first, images = dp.shard(spec_full.n, rank, world)
+        global_batch = spec_full.n
+    else:
+        first, images = 0, spec_full.n
+        global_batch = spec_full.n * world
+    spec = spec_full.with_batch(images)
+    x_host, w_host = workloads.conv_inputs(spec_full, first, images)
+
+    ctx = cabi.Context(local_rank)
+    if world > 1:
+        dp.init_comm(ctx, dist, rank, world)
+
+    n, c, h, wd, k, r, s = spec.n, spec.c, spec.h, spec.w, spec.k, spec.r, spec.s
+    geom = (n, c, h, wd, k, r, s, spec.stride, spec.pad)
+    x_count, w_count, y_count = n * c * h * wd, k * c * r * s, n * k * spec.oh * spec.ow
+    px, pw = ctx.upload(x_host), ctx.upload(w_host)
+    py, pg, pdx, pdw = ctx.alloc(y_count), ctx.alloc(y_count), ctx.alloc(x_count), ctx.alloc(w_count)
+    ctx.conv2d_fwd(px, pw, py, *geom)
+    ctx.call("katsu_cuda_add", py, py, pg, y_count)  # g = 2y, the seed sum(y*y) sends back
+    ctx.sync()
+
+    def step():
+        ctx.conv2d_fwd(px, pw, py, *geom)
+        ctx.conv2d_bwd(px, pw, pg, pdx, 0, *geom, 0)
+        ctx.conv2d_bwd(px, pw, pg, 0, pdw, *geom, 0)
+        if world > 1:
+            ctx.call("katsu_cuda_allreduce_sum", pdw, w_count)
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            import torch
+
+            dist.barrier(device_ids=[local_rank])
+            torch.cuda.synchronize()
+
+    warmup = max(args.warmup, 3)  # never fewer than three untimed steps
+    for _ in range(warmup):
+        step()
+    barrier()
+
+    ev = [[ctx.event() for _ in range(4)] for _ in range(args.steps)]
+    e_start, e_stop = ctx.event(), ctx.event()
+    launches0 = ctx.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        ctx.record(e_start)
+        for i in range(args.steps):
+            ctx.record(ev[i][0])
+            ctx.conv2d_fwd(px, pw, py, *geom)
+            ctx.record(ev[i][1])
+            ctx.conv2d_bwd(px, pw, pg, pdx, 0, *geom, 0)
+            ctx.record(ev[i][2])
+            ctx.conv2d_bwd(px, pw, pg, 0, pdw, *geom, 0)
+            ctx.record(ev[i][3])
+            if world > 1:
+                ctx.call("katsu_cuda_allreduce_sum", pdw, w_count)
+        ctx.record(e_stop)
+        ctx.sync()
+    launches = ctx.launch_count() - launches0
+    total_ms = ctx.elapsed_ms(e_start, e_stop)
+    barrier()
+    ms_per_step = total_ms / args.steps
+    parts = {"conv2d_fwd": [], "conv2d_bwd_dx": [], "conv2d_bwd_dw": []}
+    for i in range(args.steps):
+        for name, a, b in (("conv2d_fwd", 0, 1), ("conv2d_bwd_dx", 1, 2), ("conv2d_bwd_dw", 2, 3)):
+            parts[name].append(ctx.elapsed_ms(ev[i][a], ev[i][b]))
+    part_ms = {name: sum(v) / len(v) for name, v in parts.items()}
+
+    # end to end through the C ABI with host buffers: pinned x in, dX and dW out, every step
+    x_pin, dx_pin, dw_pin = ctx.pinned(x_count), ctx.pinned(x_count), ctx.pinned(w_count)
+    x_pin[:] = x_host
+
+    def e2e_step():
+        ctx.h2d(px, x_pin)
+        ctx.conv2d_fwd(px, pw, py, *geom)
+        ctx.call("katsu_cuda_add", py, py, pg, y_count)
+        ctx.conv2d_bwd(px, pw, pg, pdx, pdw, *geom, 0)
+        if world > 1:
+            ctx.call("katsu_cuda_allreduce_sum", pdw, w_count)
+        ctx.d2h(dx_pin, pdx)
+        ctx.d2h(dw_pin, pdw)
+
+    e2e_step()
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    ctx.sync()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    barrier()
+
+    if dist is not None:
+        import torch
+
+        t = torch.tensor([ms_per_step, e2e_ms], dtype=torch.float64, device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_per_step, e2e_ms = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        dominant = max(part_ms, key=part_ms.get)
+        kernel_bytes = {
+            "conv2d_fwd": 4 * (x_count + w_count + y_count),
+            "conv2d_bwd_dx": 4 * (y_count + w_count + x_count),
+            "conv2d_bwd_dw": 4 * (y_count + x_count + w_count),
+        }
+        achieved = kernel_bytes[dominant] / (part_ms[dominant] * 1e-3) / 1e9
+        step_gbs = spec.algorithmic_bytes / (ms_per_step * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": global_batch / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": spec_full.name, "x": spec_full.x_shape, "w": spec_full.w_shape,
+                       "stride": spec.stride, "padding": spec.pad, "global_batch": global_batch,
+                       "images_per_gpu": images, "parallelism": f"dp{world}",
+                       "l2": "y and g exceed L2 (inputs larger than L2, no flush)",
+                       "upstream_gradient": "g = 2y"},
+            "tflops": 6 * spec_full.with_batch(global_batch).macs / (ms_per_step * 1e-3) / 1e12,
+            "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": f"of {peak_kind}",
+                         "kernel_ms": part_ms,
+                         "step_algorithmic_gbs_per_gpu": step_gbs, "step_frac": step_gbs / peak},
+            "e2e": {"value": global_batch / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": 4 * x_count, "d2h_bytes_per_step": 4 * (x_count + w_count)},
+            "gpu_launches": launches,
+            "clocks": clocks.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(spec_full, args.cpu_sample)
+        print(json.dumps(line), flush=True)
+
+    for p in (px, pw, py, pg, pdx, pdw):
+        ctx.free(p)
+    for a in (x_pin, dx_pin, dw_pin):
+        ctx.free_pinned(a)
+    if world > 1:
+        ctx.call("katsu_cuda_comm_destroy")
+        dist.destroy_process_group()
+    ctx.close()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", default="stem_256x3x224", choices=sorted(workloads.CONV))
+    ap.add_argument("--scaling", choices=["strong", "weak"], default="strong")
+    ap.add_argument("--cpu-sample", type=int, default=32, help="images in the single-thread CPU baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (small profiling cases)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

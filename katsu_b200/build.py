@@ -76,7 +76,7 @@ def build_cuda(force: bool = False) -> str:
             fut.result()
     out = os.path.join(LIB, "libkatsu_cuda.so")
     if force or jobs or _newer(out, objects):
-        _run([nvcc, "-shared", "-o", out, *objects, "-lcudart", "-ldl"])
+        _run([nvcc, "-shared", "-cudart", "static", "-o", out, *objects, "-ldl"])
     return out
 
 

@@ -282,7 +282,8 @@ class Op:
         return Op("Conv2D", stride, padding)
 
 
-Op.Leaf, Op.Add, Op.Mul, Op.Matmul, Op.Sum = (Op(k) for k in ("Leaf", "Add", "Mul", "Matmul", "Sum"))
+Op.Leaf, Op.Add, Op.Mul, Op.Matmul, Op.Sum, Op.Reshape = (
+    Op(k) for k in ("Leaf", "Add", "Mul", "Matmul", "Sum", "Reshape"))
 
 
 class GradBorrow:
@@ -397,6 +398,15 @@ class Tensor:
         data = matmul(self._data, rhs._data, m, k, n) if count else np.zeros(0, dtype=np.float32)
         return Tensor._node(data, [m, n], Op.Matmul, [self, rhs])
 
+    def reshape(self, shape):
+        """Not in the reference (it has no view op): same flat data, new shape,
+        VJP passes the gradient through.  Mirrors the extension of the device mirror."""
+        shape = [int(d) for d in shape]
+        count = element_count(shape)
+        if count != self.numel():
+            raise DataLength(self.numel(), count)
+        return Tensor._node(self._data, shape, Op.Reshape, [self])
+
     # tensor.rs:288-306
     def _topological_order(self):
         order, visited, stack = [], set(), [(self, False)]
@@ -462,6 +472,9 @@ def _op_backward(node, g, pending):
     elif op == Op.Sum:
         target = pending[id(node._parents[0])]
         lib().ko_bcast_acc(_p(target), _p(g), _sz(target.size))
+    elif op == Op.Reshape:
+        target = pending[id(node._parents[0])]
+        lib().ko_axpy_acc(_p(target), _p(g), _sz(target.size))
     elif op == Op.Matmul:
         a, b = node._parents
         m, k, n = a._shape[0], a._shape[1], b._shape[1]

@@ -18,3 +18,13 @@ def oracle():
 
     katsu_ref.build()
     return katsu_ref
+
+
+@pytest.fixture(scope="session")
+def ctx():
+    """One C-ABI context on device 0 for the whole GPU test session."""
+    from katsu_b200 import cabi
+
+    context = cabi.Context(0)
+    yield context
+    context.close()

@@ -1,0 +1,69 @@
+"""Tensor::matmul and its VJP through the C ABI against the oracle
+(crates/katsu-core/src/tensor.rs:264-273, 418-445)."""
+import numpy as np
+import pytest
+
+from katsu_b200 import workloads
+from parity_util import REL_L2_TOL, DeviceArrays, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(2, 3, 2), (1, 1, 1), (70, 33, 65), (64, 64, 64), (129, 17, 200), (37, 2100, 10), (5, 4099, 3),
+          (66, 2048, 16), (33, 4096, 1), (3, 5000, 17), (200, 300, 12)]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_matmul_matches_oracle(ctx, oracle, shape, accumulate):
+    m, k, n = shape
+    rng = np.random.default_rng(m * 7 + k * 3 + n + accumulate)
+    a = rng.standard_normal(m * k).astype(np.float32)
+    b = rng.standard_normal(k * n).astype(np.float32)
+    g = rng.standard_normal(m * n).astype(np.float32)
+    c_ref = oracle.matmul(a, b, m, k, n, mt=True)
+    da0 = rng.standard_normal(m * k).astype(np.float32) if accumulate else np.zeros(m * k, np.float32)
+    db0 = rng.standard_normal(k * n).astype(np.float32) if accumulate else np.zeros(k * n, np.float32)
+    da_ref, db_ref = da0.copy(), db0.copy()
+    oracle.matmul_backward(a, b, g, da_ref, db_ref, m, k, n, mt=True)
+    with DeviceArrays(ctx, a=a, b=b, g=g) as d:
+        d.alloc("c", m * n, fill=np.nan)
+        if accumulate:
+            d.ptr["da"], d.ptr["db"] = ctx.upload(da0), ctx.upload(db0)
+            d.size["da"], d.size["db"] = m * k, k * n
+        else:
+            d.alloc("da", m * k, fill=np.nan), d.alloc("db", k * n, fill=np.nan)
+        ctx.matmul_fwd(d["a"], d["b"], d["c"], m, k, n)
+        ctx.matmul_bwd(d["a"], d["b"], d["g"], d["da"], d["db"], m, k, n, accumulate)
+        assert rel_l2(d.get("c"), c_ref) <= REL_L2_TOL
+        assert rel_l2(d.get("da"), da_ref) <= REL_L2_TOL
+        assert rel_l2(d.get("db"), db_ref) <= REL_L2_TOL
+
+
+def test_empty_inner_dimension(ctx):
+    """k == 0 gives a zero product and leaves the adjoints alone (tensor.rs:265, 421-423)."""
+    with DeviceArrays(ctx) as d:
+        d.alloc("c", 6, fill=5.0)
+        ctx.matmul_fwd(0, 0, d["c"], 2, 0, 3)
+        assert np.all(d.get("c") == 0.0)
+
+
+def test_classifier_head_shape(ctx, oracle):
+    """The small CNN's fully connected layer [m,65536] @ [65536,10] at a reduced batch."""
+    m, k, n = 64, workloads.CNN["fc_in"], workloads.CNN["fc_out"]
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal(m * k).astype(np.float32)
+    b = workloads.cnn_fc_weights()
+    g = rng.standard_normal(m * n).astype(np.float32)
+    c_ref = oracle.matmul(a, b, m, k, n, mt=True)
+    c64 = oracle.matmul_f64(a, b, m, k, n)
+    da64, db64 = oracle.matmul_backward_f64(a, b, g, m, k, n)
+    with DeviceArrays(ctx, a=a, b=b, g=g) as d:
+        d.alloc("c", m * n), d.alloc("da", m * k), d.alloc("db", k * n)
+        ctx.matmul_fwd(d["a"], d["b"], d["c"], m, k, n)
+        ctx.matmul_bwd(d["a"], d["b"], d["g"], d["da"], d["db"], m, k, n, 0)
+        c, da, db = d.get("c"), d.get("da"), d.get("db")
+    noise = rel_l2(c_ref, c64)  # 65536-term f32 left fold
+    assert rel_l2(c, c64) <= REL_L2_TOL
+    assert rel_l2(c, c_ref) <= REL_L2_TOL + noise
+    assert rel_l2(da, da64) <= REL_L2_TOL
+    assert rel_l2(db, db64) <= REL_L2_TOL
