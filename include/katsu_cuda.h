@@ -123,6 +123,18 @@ int32_t katsu_cuda_mul(katsu_cuda_ctx *ctx, const float *a, const float *b, floa
 /* out[0] = sum(a); Tensor::sum, tensor.rs:243-247.  Pairwise/tree order on the
  * device (the reference folds left to right). */
 int32_t katsu_cuda_sum(katsu_cuda_ctx *ctx, const float *a, float *out, size_t count);
+/* Same result as katsu_cuda_sum for callers that cannot allocate device memory (all of
+ * it belongs to the host program's own pool, or the implicit synchronisation of
+ * cudaMalloc is unacceptable).  Has no counterpart in the reference.  Its per-block
+ * partial sums live in a 16 KiB array inside the library image, held by every GPU that
+ * loads the library until exit; it calls no allocating routine.  At most
+ * KATSU_SUM_STATIC_MAX_COUNT elements, more is refused with KATSU_ERR_UNSUPPORTED.  The
+ * array is shared by all calls on a device and keeps the last call's partials: calls that
+ * overlap on the GPU (other contexts or streams of the same device) race; calls through
+ * one context are stream-ordered.  The first call on a device resolves the array's
+ * address and should come before any stream capture. */
+#define KATSU_SUM_STATIC_MAX_COUNT ((size_t)1 << 30)
+int32_t katsu_cuda_sum_static(katsu_cuda_ctx *ctx, const float *a, float *out, size_t count);
 /* dst += g : Add VJP edge (tensor.rs:400-408), adjoint accumulation
  * (tensor.rs:387-389) and gradient publication (tensor.rs:353-356). */
 int32_t katsu_cuda_axpy_acc(katsu_cuda_ctx *ctx, float *dst, const float *g, size_t count);

@@ -18,6 +18,7 @@ LIB_PATH = os.path.join(_PKG, "lib", "libkatsu_cuda.so")
 OK = 0
 ERR_INVALID_ARG, ERR_ALLOC, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_NO_DEVICE, ERR_UNSUPPORTED = range(1, 8)
 MODE_3XTF32, MODE_TF32, MODE_FP32 = 0, 1, 2
+SUM_STATIC_MAX_COUNT = 1 << 30
 COMM_ID_BYTES = 128
 
 _c_float_p = ctypes.POINTER(ctypes.c_float)
@@ -51,6 +52,7 @@ SIGNATURES = {
     "katsu_cuda_add": [_ctx, _ptr, _ptr, _ptr, _sz],
     "katsu_cuda_mul": [_ctx, _ptr, _ptr, _ptr, _sz],
     "katsu_cuda_sum": [_ctx, _ptr, _ptr, _sz],
+    "katsu_cuda_sum_static": [_ctx, _ptr, _ptr, _sz],
     "katsu_cuda_axpy_acc": [_ctx, _ptr, _ptr, _sz],
     "katsu_cuda_mul_acc": [_ctx, _ptr, _ptr, _ptr, _sz],
     "katsu_cuda_bcast_acc": [_ctx, _ptr, _ptr, _sz],

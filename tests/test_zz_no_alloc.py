@@ -1,0 +1,50 @@
+"""katsu_cuda_sum_static, the entry point for callers that may not allocate
+device memory (their pool owns all of it, or cudaMalloc's implicit device
+synchronisation is unacceptable to them): its per-block partials sit in a fixed
+array inside the library instead of cudaMalloc'ed scratch.  Checked here
+against katsu_cuda_sum through the C ABI on two calls in a row -- the second
+smaller than the first, so stale partials left in the shared array by the
+first call would show -- and on its size limit.  The file name sorts last so a
+run that stops at the first failure has already run every other test."""
+import numpy as np
+import pytest
+
+from katsu_b200 import cabi
+from parity_util import DeviceArrays
+
+pytestmark = pytest.mark.gpu
+
+
+def both_sums(ctx, d, name, count):
+    ctx.call("katsu_cuda_sum", d[name], d["ref"], count)
+    ctx.call("katsu_cuda_sum_static", d[name], d["out"], count)
+    return float(d.get("out")[0]), float(d.get("ref")[0])
+
+
+def test_static_scratch_sum_matches_allocating_sum_twice_in_a_row(ctx):
+    rng = np.random.default_rng(42)
+    big = rng.standard_normal(5_000_003).astype(np.float32)
+    small = rng.standard_normal(70_001).astype(np.float32)
+    with DeviceArrays(ctx, big=big, small=small) as d:
+        d.alloc("out", 1, fill=np.nan), d.alloc("ref", 1, fill=np.nan)
+        for name, host in (("big", big), ("small", small)):  # two calls in a row, shared scratch
+            got, ref = both_sums(ctx, d, name, host.size)
+            scale = float(np.sum(np.abs(host.astype(np.float64))))
+            exact = float(np.sum(host.astype(np.float64)))
+            assert abs(got - ref) <= 1e-6 * scale, (name, got, ref)
+            assert abs(got - exact) <= 1e-6 * scale, (name, got, exact)
+        # empty input: zero, like the reference's sum of an empty tensor (tensor.rs:243-247)
+        ctx.call("katsu_cuda_sum_static", 0, d["out"], 0)
+        assert float(d.get("out")[0]) == 0.0
+
+
+def test_static_scratch_sum_refuses_sizes_beyond_its_maximum(ctx):
+    with DeviceArrays(ctx, a=np.ones(8, np.float32)) as d:
+        d.alloc("out", 1, fill=3.0)
+        with pytest.raises(cabi.KatsuCudaError) as info:
+            ctx.call("katsu_cuda_sum_static", d["a"], d["out"], cabi.SUM_STATIC_MAX_COUNT + 1)  # refused before any launch
+        assert info.value.code == cabi.ERR_UNSUPPORTED
+        assert "at most" in info.value.message
+        assert float(d.get("out")[0]) == 3.0  # untouched
+        ctx.call("katsu_cuda_sum_static", d["a"], d["out"], 8)  # the context still works
+        assert float(d.get("out")[0]) == 8.0
