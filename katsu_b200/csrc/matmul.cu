@@ -369,6 +369,9 @@ extern "C" int32_t katsu_cuda_matmul_fwd(katsu_cuda_ctx *ctx, const float *a, co
         KATSU_NP_SWITCH(n, CALL);
 #undef CALL
     }
+    int handled = 0;
+    KATSU_TRY(katsu_umma_gemm(ctx, a, b, c, m, n, k, false, true, 0, &handled));
+    if (handled) return KATSU_OK;
     return gemm_strided(ctx, a, b, c, m, n, k, k, 1, n, 1, 0);
 }
 
@@ -393,8 +396,10 @@ extern "C" int32_t katsu_cuda_matmul_bwd(katsu_cuda_ctx *ctx, const float *a, co
 #undef CALL
             KATSU_TRY(rc);
         } else {
-            // da[m,k] = g[m,n] @ b^T : A(i,p)=g[i*n+p], B(p,j)=b[j*n+p]
-            KATSU_TRY(gemm_strided(ctx, g, b, da, m, k, n, n, 1, 1, n, accumulate));
+            // da[m,k] = g[m,n] @ b^T : A(i,p)=g[i*n+p], B(p,j)=b[j*n+p]  (both K-major for the tensor cores)
+            int handled = 0;
+            KATSU_TRY(katsu_umma_gemm(ctx, g, b, da, m, k, n, false, false, accumulate, &handled));
+            if (!handled) KATSU_TRY(gemm_strided(ctx, g, b, da, m, k, n, n, 1, 1, n, accumulate));
         }
     }
     if (db != nullptr) {
@@ -404,8 +409,10 @@ extern "C" int32_t katsu_cuda_matmul_bwd(katsu_cuda_ctx *ctx, const float *a, co
 #undef CALL
             KATSU_TRY(rc);
         } else {
-            // db[k,n] = a^T @ g : A(i,p)=a[p*k+i], B(p,j)=g[p*n+j]
-            KATSU_TRY(gemm_strided(ctx, a, g, db, k, n, m, 1, k, n, 1, accumulate));
+            // db[k,n] = a^T @ g : A(i,p)=a[p*k+i], B(p,j)=g[p*n+j]  (both MN-major for the tensor cores)
+            int handled = 0;
+            KATSU_TRY(katsu_umma_gemm(ctx, a, g, db, k, n, m, true, true, accumulate, &handled));
+            if (!handled) KATSU_TRY(gemm_strided(ctx, a, g, db, k, n, m, 1, k, n, 1, accumulate));
         }
     }
     return KATSU_OK;

@@ -9,7 +9,9 @@ from parity_util import REL_L2_TOL, DeviceArrays, rel_l2
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(2, 3, 2), (1, 1, 1), (70, 33, 65), (64, 64, 64), (129, 17, 200), (37, 2100, 10), (5, 4099, 3),
-          (66, 2048, 16), (33, 4096, 1), (3, 5000, 17), (200, 300, 12)]
+          (66, 2048, 16), (33, 4096, 1), (3, 5000, 17), (200, 300, 12),
+          # tensor-core tiles: full and ragged in every dimension, long K (split-K)
+          (128, 128, 128), (256, 512, 384), (200, 260, 132), (1000, 96, 520), (64, 4100, 36), (130, 36, 4096)]
 
 
 @pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
@@ -37,6 +39,30 @@ def test_matmul_matches_oracle(ctx, oracle, shape, accumulate):
         assert rel_l2(d.get("c"), c_ref) <= REL_L2_TOL
         assert rel_l2(d.get("da"), da_ref) <= REL_L2_TOL
         assert rel_l2(d.get("db"), db_ref) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("mode,bar", [(1, 2e-3), (2, REL_L2_TOL)], ids=["tf32", "fp32"])
+def test_matmul_precision_modes(ctx, oracle, mode, bar):
+    """TF32 mode (one tensor-core pass) holds the 2e-3 bar; FP32 mode stays on CUDA cores."""
+    m, k, n = 256, 384, 192
+    rng = np.random.default_rng(9)
+    a = rng.standard_normal(m * k).astype(np.float32)
+    b = rng.standard_normal(k * n).astype(np.float32)
+    g = rng.standard_normal(m * n).astype(np.float32)
+    c64 = oracle.matmul_f64(a, b, m, k, n)
+    da64, db64 = oracle.matmul_backward_f64(a, b, g, m, k, n)
+    ctx.set_precision(mode)
+    try:
+        with DeviceArrays(ctx, a=a, b=b, g=g) as d:
+            d.alloc("c", m * n), d.alloc("da", m * k), d.alloc("db", k * n)
+            ctx.matmul_fwd(d["a"], d["b"], d["c"], m, k, n)
+            ctx.matmul_bwd(d["a"], d["b"], d["g"], d["da"], d["db"], m, k, n, 0)
+            errors = (rel_l2(d.get("c"), c64), rel_l2(d.get("da"), da64), rel_l2(d.get("db"), db64))
+    finally:
+        ctx.set_precision(0)
+    assert max(errors) <= bar, errors
+    if mode == 1:
+        assert max(errors) > 1e-5  # really a single TF32 pass, not the split-precision path
 
 
 def test_empty_inner_dimension(ctx):
