@@ -115,6 +115,18 @@ int32_t katsu_conv_direct_dw(katsu_cuda_ctx *ctx, const float *x, const float *g
 int32_t katsu_umma_gemm(katsu_cuda_ctx *ctx, const float *a, const float *b, float *c, size_t M, size_t N, size_t K,
                         bool a_mn, bool b_mn, int accumulate, int *handled);
 
+// Wide-channel implicit-GEMM convolution on the tensor cores (conv_igemm.cu); *handled = 0
+// when the shape is outside what it takes.
+int32_t katsu_conv_igemm_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,
+                             size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                             size_t stride, size_t pad, size_t oh, size_t ow, int *handled);
+int32_t katsu_conv_igemm_dx(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx,
+                            size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                            size_t stride, size_t pad, size_t oh, size_t ow, int accumulate, int *handled);
+int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw,
+                            size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                            size_t stride, size_t pad, size_t oh, size_t ow, int accumulate, int *handled);
+
 // Low-channel 3x3 stride-1 pad-1 stencil path; *handled = 0 when the shape is
 // not one it covers (the caller then uses another kernel).
 int32_t katsu_conv_stencil_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,

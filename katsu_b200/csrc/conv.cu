@@ -1,6 +1,7 @@
 // Conv2D entry points of the C ABI: argument checks, output geometry and the
 // choice of kernel family.  The arithmetic lives in conv_stencil.cu (low
-// channel counts) and conv_direct.cu (everything else on CUDA cores).
+// channel counts), conv_igemm.cu (wide channels, tensor cores) and
+// conv_direct.cu (everything else, CUDA cores).
 #include "common.cuh"
 
 namespace {
@@ -38,6 +39,8 @@ extern "C" int32_t katsu_cuda_conv2d_fwd(katsu_cuda_ctx *ctx, const float *x, co
     int handled = 0;
     KATSU_TRY(katsu_conv_stencil_fwd(ctx, x, w, y, n, c, h, wd, k, r, s, stride, pad, &handled));
     if (handled) return KATSU_OK;
+    KATSU_TRY(katsu_conv_igemm_fwd(ctx, x, w, y, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow, &handled));
+    if (handled) return KATSU_OK;
     return katsu_conv_direct_fwd(ctx, x, w, y, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow);
 }
 
@@ -62,9 +65,15 @@ extern "C" int32_t katsu_cuda_conv2d_bwd(katsu_cuda_ctx *ctx, const float *x, co
     KATSU_TRY(katsu_conv_stencil_bwd(ctx, x, w, gr, dx, dw, n, c, h, wd, k, r, s, stride, pad, accumulate,
                                      &handled));
     if (handled) return KATSU_OK;
-    if (dx != nullptr)
-        KATSU_TRY(katsu_conv_direct_dx(ctx, w, gr, dx, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow, accumulate));
-    if (dw != nullptr)
-        KATSU_TRY(katsu_conv_direct_dw(ctx, x, gr, dw, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow, accumulate));
+    if (dx != nullptr) {
+        KATSU_TRY(katsu_conv_igemm_dx(ctx, w, gr, dx, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow, accumulate, &handled));
+        if (!handled)
+            KATSU_TRY(katsu_conv_direct_dx(ctx, w, gr, dx, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow, accumulate));
+    }
+    if (dw != nullptr) {
+        KATSU_TRY(katsu_conv_igemm_dw(ctx, x, gr, dw, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow, accumulate, &handled));
+        if (!handled)
+            KATSU_TRY(katsu_conv_direct_dw(ctx, x, gr, dw, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow, accumulate));
+    }
     return KATSU_OK;
 }

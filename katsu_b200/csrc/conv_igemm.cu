@@ -1,0 +1,652 @@
+// Wide-channel convolution as implicit GEMM on tcgen05 (forward, dX, dW).
+//
+// Reference loops: Conv2D::forward's visit closure (crates/katsu-core/src/conv2d.rs:95-103,
+// 232-262) and backward_buffers (conv2d.rs:269-292).
+//
+// Layout problem and its answer.  The reference layout is NCHW with W innermost, and a
+// filter tap shifts the window by +-1 pixel along W.  TMA cannot start a tile at an
+// address that is not 16-byte aligned, so shifted NCHW tiles cannot be fetched directly.
+// Each call therefore first copies its activation operand (x for forward and dW, g for
+// dX and dW) into a channels-innermost staging buffer [N][H][W][C]; there a tap shift
+// moves along outer dimensions (no alignment rule, out-of-range coordinates are
+// zero-filled == the reference's skipped padding taps) and a pixel's channels are one
+// contiguous K-major row.  The same pass writes the "lo" halves for 3xTF32
+// (lo = v - trunc_tf32(v); the tensor core itself truncates the raw value to "hi").
+// The transform costs 2-3 |x| of HBM traffic against a tensor-bound contraction.
+//
+//   forward : Y[pixel, oc]  = sum_tap  X[pixel + tap, c]  * Wf[tap][oc][c]     (A, B K-major)
+//   dX      : dX[pixel, c]  = sum_tap  G[(pixel + p - tap) / s, oc] * Wb[tap][c][oc]
+//             one launch per stride-parity class of input pixels      (A, B K-major)
+//   dW      : dW[tap][oc, c] = sum_pixel G[pixel, oc] * X[pixel*s + tap - p, c] (A, B MN-major)
+//
+// Tiles are 128 (two 64-pixel blocks, or 128 output channels for dW) x 128, k-blocks of
+// 32, 3-stage TMA pipeline, four rotating TMEM accumulators (see umma_gemm.cu for why).
+#include "common.cuh"
+#include "sm100.cuh"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 32, NACC = 4, STAGES = 3;
+constexpr int TILE_BYTES = BM * BK * 4;
+constexpr int MAX_TAPS = 49;
+
+__device__ __forceinline__ float lo_part(float v) { return v - __uint_as_float(__float_as_uint(v) & 0xFFFFE000u); }
+
+// ---- staging passes ---------------------------------------------------------------
+// [N][C][HW] -> [N][HW][C] through a 32x33 shared tile; optionally also the lo halves.
+__global__ void __launch_bounds__(256)
+nchw_to_nhwc_kernel(const float *__restrict__ src, float *__restrict__ dst, float *__restrict__ dst_lo, int c, int hw) {
+    __shared__ float tile[32][33];
+    const int n = blockIdx.z;
+    const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    const float *s = src + size_t(n) * c * hw;
+    for (int i = ty; i < 32; i += 8) {
+        const int cc = c0 + i, pp = p0 + tx;
+        tile[i][tx] = (cc < c && pp < hw) ? __ldg(s + size_t(cc) * hw + pp) : 0.f;
+    }
+    __syncthreads();
+    for (int i = ty; i < 32; i += 8) {
+        const int pp = p0 + i, cc = c0 + tx;
+        if (pp < hw && cc < c) {
+            const float v = tile[tx][i];
+            const size_t o = (size_t(n) * hw + pp) * c + cc;
+            dst[o] = v;
+            if (dst_lo != nullptr) dst_lo[o] = lo_part(v);
+        }
+    }
+}
+
+// w[K][C][taps] -> wf[tap][K][C] (forward B, rows = oc) and/or wb[tap][C][K] (dX B, rows = c), with lo halves.
+__global__ void __launch_bounds__(256)
+weights_to_taps_kernel(const float *__restrict__ w, float *wf, float *wf_lo, float *wb, float *wb_lo, int k, int c,
+                       int taps) {
+    const size_t total = size_t(k) * c * taps;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+        const int t = int(i % taps);
+        const int cc = int((i / taps) % c);
+        const int kk = int(i / (size_t(taps) * c));
+        const float v = w[i];
+        if (wf != nullptr) {
+            const size_t o = (size_t(t) * k + kk) * c + cc;
+            wf[o] = v;
+            if (wf_lo != nullptr) wf_lo[o] = lo_part(v);
+        }
+        if (wb != nullptr) {
+            const size_t o = (size_t(t) * c + cc) * k + kk;
+            wb[o] = v;
+            if (wb_lo != nullptr) wb_lo[o] = lo_part(v);
+        }
+    }
+}
+
+// ---- forward / dX kernel ------------------------------------------------------------
+struct IgemmParams {
+    float *out;                 // NCHW output
+    int n_img, out_c, out_h, out_w;
+    int blocks_x, blocks_y, bw, bh;  // 64-pixel blocks (bw * bh == 64) over this launch's pixel grid
+    int grid_h, grid_w;         // extent of the pixel grid (all output pixels, or one parity class)
+    int out_sy, out_oy, out_sx, out_ox;  // output pixel = (out_sy * jy + out_oy, out_sx * jx + out_ox)
+    int in_step;                // operand coordinate = j * in_step + tap offset
+    int kc;                     // channels of the operand (GEMM K per tap)
+    int ntaps;
+    int accumulate, three_pass;
+    int *status;
+    short off_y[MAX_TAPS], off_x[MAX_TAPS], b_tap[MAX_TAPS];
+};
+
+__global__ void __launch_bounds__(128, 1)
+conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_lo,
+                  const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_b_lo,
+                  const __grid_constant__ IgemmParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t full[STAGES], empty[STAGES], done;
+    __shared__ uint32_t tmem_slot;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BN;
+    const int blocks_per_img = p.blocks_x * p.blocks_y;
+    const int kchunks = (p.kc + BK - 1) / BK;
+    const int kblocks = p.ntaps * kchunks;
+    const int tiles_per_stage = p.three_pass ? 4 : 2;
+    const uint32_t stage_bytes = 4 * TILE_BYTES;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(&done, 1);
+        mbar_init_fence();
+    }
+    if (warp == 0) {
+        tmem_alloc(&tmem_slot, NACC * BN);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // block coordinates of the tile's two 64-pixel halves
+        int bn[2], by[2], bx[2];
+        for (int h = 0; h < 2; ++h) {
+            const long long gb = 2ll * blockIdx.y + h;
+            bn[h] = int(gb / blocks_per_img);  // == n_img for a block past the end: TMA zero-fills it
+            const int r = int(gb % blocks_per_img);
+            by[h] = r / p.blocks_x;
+            bx[h] = r % p.blocks_x;
+        }
+        for (int i = 0; i < kblocks; ++i) {
+            const int s = i % STAGES;
+            if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, p.status, 21)) break;
+            mbar_arrive_expect_tx(&full[s], tiles_per_stage * TILE_BYTES);
+            unsigned char *st = smem + s * stage_bytes;
+            const int t = i / kchunks, k0 = (i % kchunks) * BK;
+            for (int part = 0; part < (p.three_pass ? 2 : 1); ++part) {
+                const CUtensorMap *ma = part ? &map_a_lo : &map_a;
+                const CUtensorMap *mb = part ? &map_b_lo : &map_b;
+                for (int h = 0; h < 2; ++h)
+                    tma_load_4d(st + part * TILE_BYTES + h * (TILE_BYTES / 2), ma, &full[s], k0,
+                                bx[h] * p.bw * p.in_step + p.off_x[t], by[h] * p.bh * p.in_step + p.off_y[t], bn[h]);
+                tma_load_4d(st + (2 + part) * TILE_BYTES, mb, &full[s], k0, n0, p.b_tap[t], 0);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        const uint32_t idesc = idesc_tf32(BM, BN, false, false);
+        for (int i = 0; i < kblocks; ++i) {
+            const int s = i % STAGES;
+            if (!mbar_wait(&full[s], (i / STAGES) & 1, p.status, 22)) break;
+            tc_fence_after_sync();
+            const uint32_t st = smem_u32(smem + s * stage_bytes);
+            const uint32_t acc = tmem_base + uint32_t(i % NACC) * BN;
+            const bool first = i < NACC;
+#pragma unroll
+            for (int j = 0; j < BK / 8; ++j) {
+                const uint64_t a_hi = smem_desc(st + j * 32, 16, 1024, kLayoutSw128);
+                const uint64_t b_hi = smem_desc(st + 2 * TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
+                if (p.three_pass) {
+                    const uint64_t a_lo = smem_desc(st + TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
+                    const uint64_t b_lo = smem_desc(st + 3 * TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
+                    mma_tf32(acc, a_lo, b_hi, idesc, !(first && j == 0));
+                    mma_tf32(acc, a_hi, b_lo, idesc, true);
+                    mma_tf32(acc, a_hi, b_hi, idesc, true);
+                } else {
+                    mma_tf32(acc, a_hi, b_hi, idesc, !(first && j == 0));
+                }
+            }
+            mma_commit(&empty[s]);
+        }
+        mma_commit(&done);
+    }
+    __syncwarp();
+
+    const bool finished = mbar_wait(&done, 0, p.status, 23);
+    tc_fence_after_sync();
+    if (finished && kblocks > 0) {
+        // this thread's pixel
+        const int r = warp * 32 + lane;
+        const long long gb = 2ll * blockIdx.y + (r >> 6);
+        const int img = int(gb / blocks_per_img);
+        const int rb = int(gb % blocks_per_img);
+        const int jy = (rb / p.blocks_x) * p.bh + (r & 63) / p.bw;
+        const int jx = (rb % p.blocks_x) * p.bw + (r & 63) % p.bw;
+        const bool pixel_ok = img < p.n_img && jy < p.grid_h && jx < p.grid_w;
+        const int oy = p.out_sy * jy + p.out_oy, ox = p.out_sx * jx + p.out_ox;
+        const size_t plane = size_t(p.out_h) * p.out_w;
+        float *dst_px = p.out + size_t(img) * p.out_c * plane + size_t(oy) * p.out_w + ox;
+        const int used_acc = kblocks < NACC ? kblocks : NACC;
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            if (n0 + c0 >= p.out_c) break;
+            float v[32];
+            tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + c0, v);
+            for (int a = 1; a < used_acc; ++a) {
+                float t[32];
+                tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + a * BN + c0, t);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] += t[i];
+            }
+            if (pixel_ok) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int ch = n0 + c0 + i;
+                    if (ch < p.out_c) {
+                        float *dst = dst_px + size_t(ch) * plane;
+                        *dst = p.accumulate ? *dst + v[i] : v[i];
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, NACC * BN);
+}
+
+// ---- dW kernel ------------------------------------------------------------------------
+// One block: output tile [128 oc x 128 c] of one tap, over a range of 32-pixel groups
+// (4 rows x 8 pixels of one image).  A = G staged [pixel][oc], B = X staged
+// [pixel][c]; both MN-major (32-byte-atom swizzle).  Every DRAIN k-blocks the four
+// accumulators are folded into f32 registers so no accumulation chain exceeds 512 terms.
+struct DwParams {
+    float *partial;             // [splits][taps][K][C]
+    int n_img, k, c, taps;
+    int groups_x, groups_y;     // 8 x 4 pixel groups over the output plane
+    int groups_per_split;
+    int stride;
+    int three_pass;
+    int *status;
+    short off_y[MAX_TAPS], off_x[MAX_TAPS];
+};
+
+constexpr int DRAIN = NACC * 16;
+
+// 192 threads: warps 0-3 fold the accumulators (one TMEM lane quarter each), warp 4 feeds TMA,
+// warp 5 issues the MMAs.  The roles never share a thread, so the drain hand-shake cannot
+// wait on itself.
+__global__ void __launch_bounds__(192, 1)
+conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_g_lo,
+                     const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_x_lo,
+                     const __grid_constant__ DwParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t full[STAGES], empty[STAGES], drained, batch_done;
+    __shared__ uint32_t tmem_slot;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ctiles = (p.c + BN - 1) / BN;
+    const int c0 = (blockIdx.x % ctiles) * BN, k0 = (blockIdx.x / ctiles) * BM;
+    const int tap = blockIdx.y;
+    const int groups_per_img = p.groups_x * p.groups_y;
+    const long long total_groups = (long long)p.n_img * groups_per_img;
+    const long long g_begin = (long long)blockIdx.z * p.groups_per_split;
+    long long g_end = g_begin + p.groups_per_split;
+    if (g_end > total_groups) g_end = total_groups;
+    const int kblocks = g_end > g_begin ? int(g_end - g_begin) : 0;
+    const int tiles_per_stage = p.three_pass ? 4 : 2;
+    const uint32_t stage_bytes = 4 * TILE_BYTES;
+    const int batches = (kblocks + DRAIN - 1) / DRAIN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(&drained, 128);
+        mbar_init(&batch_done, 1);
+        mbar_init_fence();
+    }
+    if (warp == 4) {
+        tmem_alloc(&tmem_slot, NACC * BN);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 4 && lane == 0) {
+        for (int i = 0; i < kblocks; ++i) {
+            const int s = i % STAGES;
+            if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, p.status, 31)) break;
+            mbar_arrive_expect_tx(&full[s], tiles_per_stage * TILE_BYTES);
+            unsigned char *st = smem + s * stage_bytes;
+            const long long gidx = g_begin + i;
+            const int img = int(gidx / groups_per_img);
+            const int r = int(gidx % groups_per_img);
+            const int oy0 = (r / p.groups_x) * 4, ox0 = (r % p.groups_x) * 8;
+            for (int part = 0; part < (p.three_pass ? 2 : 1); ++part) {
+                const CUtensorMap *mg = part ? &map_g_lo : &map_g;
+                const CUtensorMap *mx = part ? &map_x_lo : &map_x;
+                for (int j = 0; j < BM / 32; ++j)
+                    tma_load_4d(st + part * TILE_BYTES + j * 4096, mg, &full[s], k0 + 32 * j, ox0, oy0, img);
+                for (int j = 0; j < BN / 32; ++j)
+                    tma_load_4d(st + (2 + part) * TILE_BYTES + j * 4096, mx, &full[s], c0 + 32 * j,
+                                ox0 * p.stride + p.off_x[tap], oy0 * p.stride + p.off_y[tap], img);
+            }
+        }
+    } else if (warp == 5 && lane == 0) {
+        const uint32_t idesc = idesc_tf32(BM, BN, true, true);
+        bool ok = true;
+        for (int b = 0; b < batches && ok; ++b) {
+            // the previous batch's accumulators must have been read out by all 128 threads
+            if (b > 0 && !mbar_wait(&drained, (b - 1) & 1, p.status, 33)) break;
+            tc_fence_after_sync();
+            const int i_end = (b + 1) * DRAIN < kblocks ? (b + 1) * DRAIN : kblocks;
+            for (int i = b * DRAIN; i < i_end; ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(&full[s], (i / STAGES) & 1, p.status, 32)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t st = smem_u32(smem + s * stage_bytes);
+                const int li = i - b * DRAIN;
+                const uint32_t acc = tmem_base + uint32_t(li % NACC) * BN;
+                const bool first = li < NACC;
+#pragma unroll
+                for (int j = 0; j < BK / 8; ++j) {
+                    const uint64_t a_hi = smem_desc(st + j * 1024, 4096, 512, kLayoutSw128Base32);
+                    const uint64_t b_hi = smem_desc(st + 2 * TILE_BYTES + j * 1024, 4096, 512, kLayoutSw128Base32);
+                    if (p.three_pass) {
+                        const uint64_t a_lo = smem_desc(st + TILE_BYTES + j * 1024, 4096, 512, kLayoutSw128Base32);
+                        const uint64_t b_lo = smem_desc(st + 3 * TILE_BYTES + j * 1024, 4096, 512, kLayoutSw128Base32);
+                        mma_tf32(acc, a_lo, b_hi, idesc, !(first && j == 0));
+                        mma_tf32(acc, a_hi, b_lo, idesc, true);
+                        mma_tf32(acc, a_hi, b_hi, idesc, true);
+                    } else {
+                        mma_tf32(acc, a_hi, b_hi, idesc, !(first && j == 0));
+                    }
+                }
+                mma_commit(&empty[s]);
+            }
+            if (ok) mma_commit(&batch_done);
+        }
+    }
+    __syncwarp();
+
+    if (warp < 4) {
+    // running sums of this thread's output row (oc = k0 + 32*warp + lane), 128 columns
+    float run[BN];
+#pragma unroll
+    for (int i = 0; i < BN; ++i) run[i] = 0.f;
+    bool alive = true;
+    for (int b = 0; b < batches && alive; ++b) {
+        alive = mbar_wait(&batch_done, b & 1, p.status, 34);
+        tc_fence_after_sync();
+        if (alive) {
+            const int in_batch = (kblocks - b * DRAIN) < DRAIN ? (kblocks - b * DRAIN) : DRAIN;
+            const int used_acc = in_batch < NACC ? in_batch : NACC;
+#pragma unroll
+            for (int q = 0; q < BN / 32; ++q) {
+                for (int a = 0; a < used_acc; ++a) {
+                    float t[32];
+                    tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + a * BN + q * 32, t);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) run[q * 32 + i] += t[i];
+                }
+            }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&drained);
+    }
+    {
+        const int oc = k0 + warp * 32 + lane;
+        if (oc < p.k) {
+            float *dst = p.partial + ((size_t(blockIdx.z) * p.taps + tap) * p.k + oc) * p.c;
+#pragma unroll
+            for (int i = 0; i < BN; ++i)
+                if (c0 + i < p.c) dst[c0 + i] = alive ? run[i] : 0.f;
+        }
+    }
+    }  // epilogue warps
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 4) tmem_dealloc(tmem_base, NACC * BN);
+}
+
+// dw[k][c][tap] (+)= sum over splits of partial[split][tap][k][c]
+__global__ void __launch_bounds__(256)
+dw_fold_kernel(const float *__restrict__ partial, float *dw, int k, int c, int taps, int splits, int accumulate) {
+    const size_t elems = size_t(k) * c * taps;
+    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= elems) return;
+    const int t = int(i % taps);
+    const int cc = int((i / taps) % c);
+    const int kk = int(i / (size_t(taps) * c));
+    float s = 0.f;
+    for (int q = 0; q < splits; ++q) s += partial[((size_t(q) * taps + t) * k + kk) * c + cc];
+    dw[i] = accumulate ? dw[i] + s : s;
+}
+
+// ---- host side --------------------------------------------------------------------------
+struct Scratch {
+    float *base;
+    size_t cursor;
+    float *take(size_t n) {
+        float *ptr = base + cursor;
+        cursor += (n + 63) / 64 * 64;  // keeps every array 256-byte aligned
+        return ptr;
+    }
+};
+
+size_t padded(size_t n) { return (n + 63) / 64 * 64; }
+
+// [N][H][W][C] staging array as a 4-D tensor map, box {32 channels, bw, bh, 1}; step > 1 walks every step-th pixel.
+bool nhwc_map(CUtensorMap *map, const float *base, size_t n, size_t h, size_t w, size_t c, int bw, int bh, int step,
+              CUtensorMapSwizzle swizzle) {
+    katsu_tensor_map_encode_fn encode = katsu_tensor_map_encoder();
+    if (encode == nullptr) return false;
+    cuuint64_t dims[4] = {c, w, h, n};
+    cuuint64_t strides[3] = {c * sizeof(float), w * c * sizeof(float), h * w * c * sizeof(float)};
+    cuuint32_t box[4] = {32, cuuint32_t((bw - 1) * step + 1), cuuint32_t((bh - 1) * step + 1), 1};
+    cuuint32_t estr[4] = {1, cuuint32_t(step), cuuint32_t(step), 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// [taps][rows][inner] weight staging array, box {32, 128, 1, 1} (4-D with a unit last dimension).
+bool taps_map(CUtensorMap *map, const float *base, size_t taps, size_t rows, size_t inner) {
+    katsu_tensor_map_encode_fn encode = katsu_tensor_map_encoder();
+    if (encode == nullptr) return false;
+    cuuint64_t dims[4] = {inner, rows, taps, 1};
+    cuuint64_t strides[3] = {inner * sizeof(float), rows * inner * sizeof(float), taps * rows * inner * sizeof(float)};
+    cuuint32_t box[4] = {32, BN, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int32_t stage_nhwc(katsu_cuda_ctx *ctx, const float *src, float *dst, float *dst_lo, size_t n, size_t c, size_t hw) {
+    dim3 grid((unsigned)katsu_div_up(hw, 32), (unsigned)katsu_div_up(c, 32), (unsigned)n);
+    KATSU_LAUNCH(ctx, nchw_to_nhwc_kernel, grid, 256, 0, src, dst, dst_lo, (int)c, (int)hw);
+    return KATSU_OK;
+}
+
+void pick_block(size_t width, int *bw, int *bh) {
+    *bw = (width % 32 == 0) ? 32 : (width % 16 == 0) ? 16 : 8;
+    *bh = 64 / *bw;
+}
+
+constexpr size_t kSmemBytes = size_t(STAGES) * 4 * TILE_BYTES + 1024;
+
+struct Shape {
+    size_t n, c, h, w, k, r, s, stride, pad, oh, ow;
+};
+
+bool igemm_shape(const katsu_cuda_ctx *ctx, const Shape &g) {
+    if (ctx->precision == KATSU_MODE_FP32) return false;
+    if (g.c < 16 || g.k < 16 || (g.c & 3) || (g.k & 3)) return false;  // TMA needs 16-byte channel rows
+    if (g.r * g.s > (size_t)MAX_TAPS || g.stride > 8 || g.pad > 1024) return false;
+    if (g.n > 65535 || g.h > 32768 || g.w > 32768) return false;
+    // too little work for 128x128 tiles: leave it to the direct kernels
+    if (g.n * g.oh * g.ow < 64) return false;
+    return katsu_tensor_map_encoder() != nullptr;
+}
+
+}  // namespace
+
+int32_t katsu_conv_igemm_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,
+                             size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                             size_t stride, size_t pad, size_t oh, size_t ow, int *handled) {
+    *handled = 0;
+    const Shape g = {n, c, h, wd, k, r, s, stride, pad, oh, ow};
+    if (!igemm_shape(ctx, g)) return KATSU_OK;
+    *handled = 1;
+    const bool three = ctx->precision == KATSU_MODE_3XTF32;
+    const size_t xe = n * c * h * wd, we = k * c * r * s, taps = r * s;
+    float *base = nullptr;
+    KATSU_TRY(katsu_scratch(ctx, (padded(xe) + padded(we)) * (three ? 2 : 1), &base));
+    Scratch sc = {base, 0};
+    float *xt = sc.take(xe), *xt_lo = three ? sc.take(xe) : nullptr;
+    float *wf = sc.take(we), *wf_lo = three ? sc.take(we) : nullptr;
+    KATSU_TRY(stage_nhwc(ctx, x, xt, xt_lo, n, c, h * wd));
+    KATSU_LAUNCH(ctx, weights_to_taps_kernel, (unsigned)katsu_div_up(we, 256), 256, 0, w, wf, wf_lo, (float *)nullptr,
+                 (float *)nullptr, (int)k, (int)c, (int)taps);
+
+    IgemmParams p;
+    p.out = y;
+    p.n_img = (int)n; p.out_c = (int)k; p.out_h = (int)oh; p.out_w = (int)ow;
+    pick_block(ow, &p.bw, &p.bh);
+    p.blocks_x = (int)katsu_div_up(ow, (size_t)p.bw);
+    p.blocks_y = (int)katsu_div_up(oh, (size_t)p.bh);
+    p.grid_h = (int)oh; p.grid_w = (int)ow;
+    p.out_sy = 1; p.out_oy = 0; p.out_sx = 1; p.out_ox = 0;
+    p.in_step = (int)stride;
+    p.kc = (int)c;
+    p.ntaps = (int)taps;
+    p.accumulate = 0;
+    p.three_pass = three ? 1 : 0;
+    p.status = ctx->status;
+    for (size_t t = 0; t < taps; ++t) {
+        p.off_y[t] = (short)((int)(t / s) - (int)pad);
+        p.off_x[t] = (short)((int)(t % s) - (int)pad);
+        p.b_tap[t] = (short)t;
+    }
+    CUtensorMap ma, ma_lo, mb, mb_lo;
+    bool ok = nhwc_map(&ma, xt, n, h, wd, c, p.bw, p.bh, (int)stride, CU_TENSOR_MAP_SWIZZLE_128B) &&
+              nhwc_map(&ma_lo, three ? xt_lo : xt, n, h, wd, c, p.bw, p.bh, (int)stride, CU_TENSOR_MAP_SWIZZLE_128B) &&
+              taps_map(&mb, wf, taps, k, c) && taps_map(&mb_lo, three ? wf_lo : wf, taps, k, c);
+    if (!ok) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv forward)");
+    KATSU_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    const size_t total_blocks = n * p.blocks_x * p.blocks_y;
+    dim3 grid((unsigned)katsu_div_up(k, (size_t)BN), (unsigned)katsu_div_up(total_blocks, 2));
+    KATSU_LAUNCH(ctx, conv_igemm_kernel, grid, 128, kSmemBytes, ma, ma_lo, mb, mb_lo, p);
+    return KATSU_OK;
+}
+
+int32_t katsu_conv_igemm_dx(katsu_cuda_ctx *ctx, const float *w, const float *gr, float *dx,
+                            size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                            size_t stride, size_t pad, size_t oh, size_t ow, int accumulate, int *handled) {
+    *handled = 0;
+    const Shape g = {n, c, h, wd, k, r, s, stride, pad, oh, ow};
+    if (!igemm_shape(ctx, g)) return KATSU_OK;
+    *handled = 1;
+    const bool three = ctx->precision == KATSU_MODE_3XTF32;
+    const size_t ge = n * k * oh * ow, we = k * c * r * s, taps = r * s;
+    float *base = nullptr;
+    KATSU_TRY(katsu_scratch(ctx, (padded(ge) + padded(we)) * (three ? 2 : 1), &base));
+    Scratch sc = {base, 0};
+    float *gt = sc.take(ge), *gt_lo = three ? sc.take(ge) : nullptr;
+    float *wb = sc.take(we), *wb_lo = three ? sc.take(we) : nullptr;
+    KATSU_TRY(stage_nhwc(ctx, gr, gt, gt_lo, n, k, oh * ow));
+    KATSU_LAUNCH(ctx, weights_to_taps_kernel, (unsigned)katsu_div_up(we, 256), 256, 0, w, (float *)nullptr,
+                 (float *)nullptr, wb, wb_lo, (int)k, (int)c, (int)taps);
+    KATSU_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+
+    // One launch per parity class (py, px) of input pixels: iy = stride*jy + py receives
+    // only taps with (py + pad - ky) divisible by stride, from g row jy + (py + pad - ky)/stride.
+    const int st = (int)stride;
+    // A class no tap reaches (stride larger than the filter) receives nothing: zero dx once
+    // and let every launch add.
+    bool some_class_empty = false;
+    for (int py = 0; py < st; ++py) {
+        bool any = false;
+        for (int ky = 0; ky < (int)r; ++ky) any |= (((py + (int)pad - ky) % st) + st) % st == 0;
+        some_class_empty |= !any;
+    }
+    for (int px = 0; px < st; ++px) {
+        bool any = false;
+        for (int kx = 0; kx < (int)s; ++kx) any |= (((px + (int)pad - kx) % st) + st) % st == 0;
+        some_class_empty |= !any;
+    }
+    if (some_class_empty && !accumulate) {
+        KATSU_CUDA_TRY(cudaMemsetAsync(dx, 0, n * c * h * wd * sizeof(float), ctx->stream));
+        accumulate = 1;
+    }
+    for (int py = 0; py < st && py < (int)h; ++py)
+        for (int px = 0; px < st && px < (int)wd; ++px) {
+            IgemmParams p;
+            p.out = dx;
+            p.n_img = (int)n; p.out_c = (int)c; p.out_h = (int)h; p.out_w = (int)wd;
+            p.grid_h = (int)((h - py + st - 1) / st);
+            p.grid_w = (int)((wd - px + st - 1) / st);
+            pick_block((size_t)p.grid_w, &p.bw, &p.bh);
+            p.blocks_x = (p.grid_w + p.bw - 1) / p.bw;
+            p.blocks_y = (p.grid_h + p.bh - 1) / p.bh;
+            p.out_sy = st; p.out_oy = py; p.out_sx = st; p.out_ox = px;
+            p.in_step = 1;
+            p.kc = (int)k;
+            p.accumulate = accumulate;
+            p.three_pass = three ? 1 : 0;
+            p.status = ctx->status;
+            int nt = 0;
+            for (int ky = 0; ky < (int)r; ++ky) {
+                const int ty = py + (int)pad - ky;
+                if (((ty % st) + st) % st != 0) continue;
+                for (int kx = 0; kx < (int)s; ++kx) {
+                    const int tx = px + (int)pad - kx;
+                    if (((tx % st) + st) % st != 0) continue;
+                    // floor division (ty, tx may be negative)
+                    p.off_y[nt] = (short)((ty >= 0) ? ty / st : -((-ty + st - 1) / st));
+                    p.off_x[nt] = (short)((tx >= 0) ? tx / st : -((-tx + st - 1) / st));
+                    p.b_tap[nt] = (short)(ky * (int)s + kx);
+                    ++nt;
+                }
+            }
+            p.ntaps = nt;
+            if (nt == 0) continue;
+            const size_t total_blocks = n * p.blocks_x * p.blocks_y;
+            CUtensorMap ma, ma_lo, mb, mb_lo;
+            bool ok = nhwc_map(&ma, gt, n, oh, ow, k, p.bw, p.bh, 1, CU_TENSOR_MAP_SWIZZLE_128B) &&
+                      nhwc_map(&ma_lo, three ? gt_lo : gt, n, oh, ow, k, p.bw, p.bh, 1, CU_TENSOR_MAP_SWIZZLE_128B) &&
+                      taps_map(&mb, wb, taps, c, k) && taps_map(&mb_lo, three ? wb_lo : wb, taps, c, k);
+            if (!ok) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv dX)");
+            dim3 grid((unsigned)katsu_div_up(c, (size_t)BN), (unsigned)katsu_div_up(total_blocks, 2));
+            KATSU_LAUNCH(ctx, conv_igemm_kernel, grid, 128, kSmemBytes, ma, ma_lo, mb, mb_lo, p);
+        }
+    return KATSU_OK;
+}
+
+int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr, float *dw,
+                            size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                            size_t stride, size_t pad, size_t oh, size_t ow, int accumulate, int *handled) {
+    *handled = 0;
+    const Shape g = {n, c, h, wd, k, r, s, stride, pad, oh, ow};
+    if (!igemm_shape(ctx, g)) return KATSU_OK;
+    *handled = 1;
+    const bool three = ctx->precision == KATSU_MODE_3XTF32;
+    const size_t xe = n * c * h * wd, ge = n * k * oh * ow, taps = r * s;
+    DwParams p;
+    p.n_img = (int)n; p.k = (int)k; p.c = (int)c; p.taps = (int)taps;
+    p.groups_x = (int)katsu_div_up(ow, 8);
+    p.groups_y = (int)katsu_div_up(oh, 4);
+    p.stride = (int)stride;
+    p.three_pass = three ? 1 : 0;
+    p.status = ctx->status;
+    for (size_t t = 0; t < taps; ++t) {
+        p.off_y[t] = (short)((int)(t / s) - (int)pad);
+        p.off_x[t] = (short)((int)(t % s) - (int)pad);
+    }
+    const size_t total_groups = n * p.groups_x * p.groups_y;
+    const size_t out_tiles = katsu_div_up(k, (size_t)BM) * katsu_div_up(c, (size_t)BN) * taps;
+    size_t splits = katsu_div_up(size_t(ctx->num_sms) * 2, out_tiles);
+    if (splits > total_groups) splits = total_groups;
+    if (splits < 1) splits = 1;
+    p.groups_per_split = (int)katsu_div_up(total_groups, splits);
+    splits = katsu_div_up(total_groups, (size_t)p.groups_per_split);
+
+    const size_t partial_e = splits * taps * k * c;
+    float *base = nullptr;
+    KATSU_TRY(katsu_scratch(ctx, (padded(xe) + padded(ge)) * (three ? 2 : 1) + padded(partial_e), &base));
+    Scratch sc = {base, 0};
+    float *xt = sc.take(xe), *xt_lo = three ? sc.take(xe) : nullptr;
+    float *gt = sc.take(ge), *gt_lo = three ? sc.take(ge) : nullptr;
+    p.partial = sc.take(partial_e);
+    KATSU_TRY(stage_nhwc(ctx, x, xt, xt_lo, n, c, h * wd));
+    KATSU_TRY(stage_nhwc(ctx, gr, gt, gt_lo, n, k, oh * ow));
+
+    CUtensorMap mg, mg_lo, mx, mx_lo;
+    const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+    bool ok = nhwc_map(&mg, gt, n, oh, ow, k, 8, 4, 1, sw) && nhwc_map(&mg_lo, three ? gt_lo : gt, n, oh, ow, k, 8, 4, 1, sw) &&
+              nhwc_map(&mx, xt, n, h, wd, c, 8, 4, (int)stride, sw) &&
+              nhwc_map(&mx_lo, three ? xt_lo : xt, n, h, wd, c, 8, 4, (int)stride, sw);
+    if (!ok) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv dW)");
+    KATSU_CUDA_TRY(cudaFuncSetAttribute(conv_dw_igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    dim3 grid((unsigned)(katsu_div_up(k, (size_t)BM) * katsu_div_up(c, (size_t)BN)), (unsigned)taps, (unsigned)splits);
+    KATSU_LAUNCH(ctx, conv_dw_igemm_kernel, grid, 192, kSmemBytes, mg, mg_lo, mx, mx_lo, p);
+    KATSU_LAUNCH(ctx, dw_fold_kernel, (unsigned)katsu_div_up(k * c * taps, (size_t)256), 256, 0, p.partial, dw, (int)k,
+                 (int)c, (int)taps, (int)splits, accumulate);
+    return KATSU_OK;
+}

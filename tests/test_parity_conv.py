@@ -17,6 +17,11 @@ SHAPES = [
     (1, 1, 3, 3, 1, 2, 2, 1, 0), (1, 1, 1, 1, 1, 1, 1, 1, 0), (3, 5, 9, 7, 6, 3, 3, 2, 1),
     (2, 8, 6, 6, 5, 1, 1, 1, 0), (1, 3, 10, 10, 4, 5, 5, 3, 2), (1, 7, 13, 11, 9, 3, 3, 1, 1),
     (2, 16, 12, 12, 24, 3, 3, 1, 1), (2, 16, 13, 12, 24, 3, 3, 2, 1), (1, 4, 5, 5, 3, 3, 3, 1, 2),
+    # tensor-core implicit GEMM: channel counts that are multiples of 4 and >= 16; ragged tiles,
+    # strides (parity classes in dX), rectangular and 1x1 / 5x5 filters, a stride larger than the filter
+    (1, 32, 20, 20, 64, 3, 3, 1, 1), (2, 64, 15, 17, 40, 3, 3, 2, 1), (1, 20, 9, 9, 36, 5, 5, 1, 2),
+    (1, 16, 8, 8, 16, 1, 1, 1, 0), (1, 16, 9, 9, 16, 1, 1, 3, 0), (2, 36, 10, 10, 132, 3, 3, 1, 1),
+    (1, 16, 10, 12, 16, 2, 3, 1, 1), (3, 160, 7, 9, 144, 3, 3, 1, 1), (1, 24, 33, 32, 20, 3, 3, 2, 1),
     # stencil path: C in 1..4, 3x3, stride 1, pad 1
     (1, 3, 8, 8, 8, 3, 3, 1, 1), (2, 3, 33, 37, 5, 3, 3, 1, 1), (1, 1, 40, 64, 70, 3, 3, 1, 1),
     (2, 4, 9, 36, 9, 3, 3, 1, 1), (3, 2, 17, 5, 64, 3, 3, 1, 1), (2, 3, 64, 64, 32, 3, 3, 1, 1),
@@ -54,6 +59,33 @@ def test_conv_matches_oracle(ctx, oracle, shape, accumulate):
     errors = run_case(ctx, oracle, shape, accumulate, np.random.default_rng(sum(shape) + accumulate))
     for name, err in errors.items():
         assert err <= REL_L2_TOL, (name, err, shape)
+
+
+@pytest.mark.parametrize("shape", [(2, 32, 14, 14, 48, 3, 3, 1, 1), (1, 64, 16, 16, 32, 3, 3, 2, 1)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_conv_tf32_mode(ctx, oracle, shape):
+    """Opt-in single-pass TF32 mode on the tensor-core path: within 2e-3, and measurably
+    coarser than the default split-precision mode (so the switch really selects it)."""
+    n, c, h, w, k, r, s, stride, pad = shape
+    rng = np.random.default_rng(17)
+    xs, ws = [n, c, h, w], [k, c, r, s]
+    oh, ow = oracle.conv_out_dims(h, w, r, s, stride, pad)
+    x = rng.standard_normal(n * c * h * w).astype(np.float32)
+    wt = rng.standard_normal(k * c * r * s).astype(np.float32)
+    g = rng.standard_normal(n * k * oh * ow).astype(np.float32)
+    y64 = oracle.conv2d_forward_f64(x, wt, xs, ws, stride, pad)
+    dx64, dw64 = oracle.conv2d_backward_f64(x, wt, g, xs, ws, stride, pad)
+    ctx.set_precision(1)
+    try:
+        with DeviceArrays(ctx, x=x, w=wt, g=g) as d:
+            d.alloc("y", y64.size), d.alloc("dx", x.size), d.alloc("dw", wt.size)
+            ctx.conv2d_fwd(d["x"], d["w"], d["y"], n, c, h, w, k, r, s, stride, pad)
+            ctx.conv2d_bwd(d["x"], d["w"], d["g"], d["dx"], d["dw"], n, c, h, w, k, r, s, stride, pad, 0)
+            errors = (rel_l2(d.get("y"), y64), rel_l2(d.get("dx"), dx64), rel_l2(d.get("dw"), dw64))
+    finally:
+        ctx.set_precision(0)
+    assert max(errors) <= 2e-3, errors
+    assert min(errors) > 1e-5, errors
 
 
 def test_skipping_one_output_leaves_the_other_unchanged(ctx, oracle):
