@@ -127,6 +127,11 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *g,
                             size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
                             size_t stride, size_t pad, size_t oh, size_t ow, int accumulate, int *handled);
 
+// Low-channel (C <= 3) 3x3 stride-1 pad-1 convolution on the tensor cores (conv_stem_tc.cu).
+int32_t katsu_conv_stem_tc_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,
+                               size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                               size_t stride, size_t pad, int *handled);
+
 // Low-channel 3x3 stride-1 pad-1 stencil path; *handled = 0 when the shape is
 // not one it covers (the caller then uses another kernel).
 int32_t katsu_conv_stencil_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,

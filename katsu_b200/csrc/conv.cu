@@ -37,6 +37,8 @@ extern "C" int32_t katsu_cuda_conv2d_fwd(katsu_cuda_ctx *ctx, const float *x, co
     if (n == 0) return KATSU_OK;  // empty batch: y has no elements (conv2d.rs:195-196)
     KATSU_REQUIRE(x != nullptr && w != nullptr && y != nullptr, "null tensor");
     int handled = 0;
+    KATSU_TRY(katsu_conv_stem_tc_fwd(ctx, x, w, y, n, c, h, wd, k, r, s, stride, pad, &handled));
+    if (handled) return KATSU_OK;
     KATSU_TRY(katsu_conv_stencil_fwd(ctx, x, w, y, n, c, h, wd, k, r, s, stride, pad, &handled));
     if (handled) return KATSU_OK;
     KATSU_TRY(katsu_conv_igemm_fwd(ctx, x, w, y, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow, &handled));

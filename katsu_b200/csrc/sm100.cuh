@@ -30,6 +30,30 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// Shared-memory stores through the shared window.  Pointers derived from the manually
+// aligned dynamic shared-memory base are generic to the compiler, and generic stores that
+// land in shared memory were measured ~7x slower than st.shared on this part.
+__device__ __forceinline__ void st_shared_f32(void *p, float v) {
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(smem_u32(p)), "f"(v) : "memory");
+}
+
+__device__ __forceinline__ float ld_shared_f32(const void *p) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(smem_u32(p)) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ float4 ld_shared_v4(const void *p) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_u32(p)) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_shared_v4(void *p, float4 v) {
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(smem_u32(p)), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+
 // ---- mbarrier ---------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t arrivals) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(arrivals) : "memory");
@@ -73,10 +97,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *s
     const long long start = clock64();
     for (uint32_t i = 0; i < kWaitPolls; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+#ifdef KATSU_WAIT_SLEEP
+        __nanosleep(KATSU_WAIT_SLEEP);
+#endif
         if ((i & 63u) == 63u && clock64() - start > kWaitCycles) break;
     }
     if (status != nullptr) atomicCAS(status, 0, code);
     return false;
+}
+
+// Whole-warp wait: lane 0 polls, the warp then reconverges.  32 lanes polling one
+// barrier are 32 separate shared-memory transactions per poll, enough to starve the
+// shared-memory pipe of a block whose other warps are storing tiles.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, int *status, int code) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, status, code) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);  // also orders lane 0's acquire before the other lanes' accesses
+    return ok != 0;
 }
 
 // Orders generic-proxy writes to shared memory before async-proxy reads (tcgen05.mma, TMA stores).
@@ -104,6 +141,35 @@ __device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *m
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
         "r"(c2), "r"(c3)
         : "memory");
+}
+
+// Tensor store shared -> global (bulk async group).  Out-of-range parts of the box are
+// clipped.  The issuing thread must commit the group and, before the shared buffer is
+// overwritten, wait until the group has finished reading it.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, const void *smem_src, int c0, int c1, int c2,
+                                             int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+
+// Waits until at most `Pending` of this thread's committed store groups still read shared memory.
+template <int Pending>
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(Pending) : "memory");
+}
+
+template <int Pending>
+__device__ __forceinline__ void tma_store_wait_all() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(Pending) : "memory");
+}
+
+// Barrier among a subset of the block's warps (id 1..15, thread count a multiple of 32).
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 // ---- tensor memory ------------------------------------------------------------
@@ -144,6 +210,28 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+
+// Registers -> tensor memory, same shape as tmem_ld_32x32.  The stores are complete (visible
+// to a later tcgen05.mma after the usual fence / barrier hand-off) once tmem_st_wait returns.
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
+        "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])),
+        "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
+        "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---- tcgen05.mma --------------------------------------------------------------
 // Shared-memory matrix descriptor, 128-byte swizzle.  `addr` is the shared
@@ -198,6 +286,20 @@ __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t desc_a, uint6
         : "memory");
 }
 
+// Same with the A operand in tensor memory (lane = row, one 32-bit column per K element;
+// A is always K-major in this form).
+__device__ __forceinline__ void mma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                            bool accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n"
+        "}\n"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate ? 1u : 0u)
+        : "memory");
+}
+
 // Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -231,6 +333,7 @@ static inline katsu_tensor_map_encode_fn katsu_tensor_map_encoder() {
 static inline bool katsu_make_tensor_map(CUtensorMap *map, const float *base, int rank, const uint64_t *dims,
                                          const uint64_t *strides_elems, const uint32_t *box,
                                          CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+    if (rank < 1 || rank > 5) return false;
     katsu_tensor_map_encode_fn encode = katsu_tensor_map_encoder();
     if (encode == nullptr) return false;
     cuuint64_t gdims[5], gstrides[4];

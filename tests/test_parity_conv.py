@@ -88,6 +88,19 @@ def test_conv_tf32_mode(ctx, oracle, shape):
     assert min(errors) > 1e-5, errors
 
 
+@pytest.mark.parametrize("shape", [s for s in SHAPES if s[1] <= 4 and s[5:] == (3, 3, 1, 1)] + [(2, 32, 12, 12, 24, 3, 3, 1, 1)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_conv_fp32_mode_uses_cuda_cores(ctx, oracle, shape):
+    """KATSU_MODE_FP32 keeps every contraction on the FP32 pipe (stencil and direct kernels)."""
+    ctx.set_precision(2)
+    try:
+        errors = run_case(ctx, oracle, shape, 0, np.random.default_rng(sum(shape)))
+    finally:
+        ctx.set_precision(0)
+    for name, err in errors.items():
+        assert err <= REL_L2_TOL, (name, err, shape)
+
+
 def test_skipping_one_output_leaves_the_other_unchanged(ctx, oracle):
     n, c, h, w, k, r, s, stride, pad = 2, 3, 20, 36, 16, 3, 3, 1, 1
     rng = np.random.default_rng(5)
