@@ -132,6 +132,13 @@ int32_t katsu_conv_stem_tc_fwd(katsu_cuda_ctx *ctx, const float *x, const float 
                                size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
                                size_t stride, size_t pad, int *handled);
 
+// TMA-fed dX stencil (conv_stencil_tma.cu); *handled = 0 when TMA cannot describe g.
+int32_t katsu_stencil_dx_tma(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx, size_t n, size_t c,
+                             size_t h, size_t wd, size_t k, int accumulate, int *handled);
+
+int32_t katsu_stencil_dw_tma(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw, size_t n, size_t c,
+                             size_t h, size_t wd, size_t k, int accumulate, int *handled);
+
 // Low-channel 3x3 stride-1 pad-1 stencil path; *handled = 0 when the shape is
 // not one it covers (the caller then uses another kernel).
 int32_t katsu_conv_stencil_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,

@@ -438,7 +438,9 @@ int32_t katsu_conv_stencil_bwd(katsu_cuda_ctx *ctx, const float *x, const float 
     if (!stencil_shape(n, c, h, wd, k, r, s, stride, pad)) return KATSU_OK;
     *handled = 1;
     StencilDims d = {(int)n, (int)k, (int)h, (int)wd, (int)katsu_div_up(wd, (size_t)TW), 0};
-    if (dx != nullptr) {
+    int dx_done = 0;
+    if (dx != nullptr) KATSU_TRY(katsu_stencil_dx_tma(ctx, w, g, dx, n, c, h, wd, k, accumulate, &dx_done));
+    if (dx != nullptr && !dx_done) {
         switch (c) {
             case 1: KATSU_TRY(dx_launch<1>(ctx, w, g, dx, d, accumulate)); break;
             case 2: KATSU_TRY(dx_launch<2>(ctx, w, g, dx, d, accumulate)); break;
@@ -446,7 +448,9 @@ int32_t katsu_conv_stencil_bwd(katsu_cuda_ctx *ctx, const float *x, const float 
             default: KATSU_TRY(dx_launch<4>(ctx, w, g, dx, d, accumulate)); break;
         }
     }
-    if (dw != nullptr) {
+    int dw_done = 0;
+    if (dw != nullptr) KATSU_TRY(katsu_stencil_dw_tma(ctx, x, g, dw, n, c, h, wd, k, accumulate, &dw_done));
+    if (dw != nullptr && !dw_done) {
         switch (c) {
             case 1: KATSU_TRY(dw_launch<1>(ctx, x, g, dw, d, accumulate)); break;
             case 2: KATSU_TRY(dw_launch<2>(ctx, x, g, dw, d, accumulate)); break;
