@@ -260,19 +260,41 @@ def run_ours(args):
             parts[name].append(ctx.elapsed_ms(ev[i][a], ev[i][b]))
     part_ms = {name: sum(v) / len(v) for name, v in parts.items()}
 
-    # end to end through the C ABI with host buffers: pinned x in, dX and dW out, every step
+    # End to end through the C ABI with HOST buffers: pinned x in, dX and dW out, every step.
+    # The batch is cut into chunks that alternate between two contexts (streams) of the same
+    # device, so chunk i+1's host->device copy and chunk i-1's device->host copy overlap chunk
+    # i's kernels -- what a caller with a data loader does.  dW partials of the two contexts are
+    # added at the end (and all-reduced across ranks).
+    for p in (py, pg, pdx):
+        ctx.free(p)
     x_pin, dx_pin, dw_pin = ctx.pinned(x_count), ctx.pinned(x_count), ctx.pinned(w_count)
     x_pin[:] = x_host
+    lanes = [ctx, cabi.Context(local_rank)]
+    n_chunks = min(8, n) if n >= 2 else 1
+    bounds = [dp.shard(n, i, n_chunks) for i in range(n_chunks)]
+    per_img_x, per_img_y = c * h * wd, k * spec.oh * spec.ow
+    chunk_max = max(cnt for _, cnt in bounds)
+    lane_buf = []
+    for lane_ctx in lanes:
+        lane_buf.append({"w": lane_ctx.upload(w_host), "x": lane_ctx.alloc(chunk_max * per_img_x),
+                         "y": lane_ctx.alloc(chunk_max * per_img_y), "g": lane_ctx.alloc(chunk_max * per_img_y),
+                         "dx": lane_ctx.alloc(chunk_max * per_img_x), "dw": lane_ctx.alloc(w_count)})
 
     def e2e_step():
-        ctx.h2d(px, x_pin)
-        ctx.conv2d_fwd(px, pw, py, *geom)
-        ctx.call("katsu_cuda_add", py, py, pg, y_count)
-        ctx.conv2d_bwd(px, pw, pg, pdx, pdw, *geom, 0)
+        for i, (first_img, cnt) in enumerate(bounds):
+            lane_ctx, b = lanes[i % 2], lane_buf[i % 2]
+            cg = (cnt, c, h, wd, k, r, s, spec.stride, spec.pad)
+            lane_ctx.h2d(b["x"], x_pin[first_img * per_img_x:(first_img + cnt) * per_img_x])
+            lane_ctx.conv2d_fwd(b["x"], b["w"], b["y"], *cg)
+            lane_ctx.call("katsu_cuda_add", b["y"], b["y"], b["g"], cnt * per_img_y)
+            lane_ctx.conv2d_bwd(b["x"], b["w"], b["g"], b["dx"], b["dw"], *cg, 1 if i >= 2 else 0)
+            lane_ctx.d2h_async(dx_pin[first_img * per_img_x:(first_img + cnt) * per_img_x], b["dx"])
+        lanes[1].sync()
+        if n_chunks > 1:
+            ctx.call("katsu_cuda_axpy_acc", lane_buf[0]["dw"], lane_buf[1]["dw"], w_count)
         if world > 1:
-            ctx.call("katsu_cuda_allreduce_sum", pdw, w_count)
-        ctx.d2h(dx_pin, pdx)
-        ctx.d2h(dw_pin, pdw)
+            ctx.call("katsu_cuda_allreduce_sum", lane_buf[0]["dw"], w_count)
+        ctx.d2h(dw_pin, lane_buf[0]["dw"])
 
     e2e_step()
     barrier()
@@ -316,7 +338,8 @@ def run_ours(args):
                          "kernel_ms": part_ms,
                          "step_algorithmic_gbs_per_gpu": step_gbs, "step_frac": step_gbs / peak},
             "e2e": {"value": global_batch / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": 4 * x_count, "d2h_bytes_per_step": 4 * (x_count + w_count)},
+                    "h2d_bytes_per_step": 4 * x_count, "d2h_bytes_per_step": 4 * (x_count + w_count),
+                    "pipeline": f"{n_chunks} batch chunks over 2 streams, pinned host buffers"},
             "gpu_launches": launches,
             "clocks": clocks.summary(),
         }
@@ -324,10 +347,14 @@ def run_ours(args):
             line["cpu_baseline"] = cpu_baseline(spec_full, args.cpu_sample)
         print(json.dumps(line), flush=True)
 
-    for p in (px, pw, py, pg, pdx, pdw):
+    for p in (px, pw, pdw):
         ctx.free(p)
+    for lane_ctx, b in zip(lanes, lane_buf):
+        for p in b.values():
+            lane_ctx.free(p)
     for a in (x_pin, dx_pin, dw_pin):
         ctx.free_pinned(a)
+    lanes[1].close()
     if world > 1:
         ctx.call("katsu_cuda_comm_destroy")
         dist.destroy_process_group()

@@ -75,6 +75,10 @@ int32_t katsu_cuda_zero(katsu_cuda_ctx *ctx, float *dst, size_t count);
  * stream; h2d is ordered on the stream and returns once the source is consumed. */
 int32_t katsu_cuda_h2d(katsu_cuda_ctx *ctx, float *dst_device, const float *src_host, size_t count);
 int32_t katsu_cuda_d2h(katsu_cuda_ctx *ctx, float *dst_host, const float *src_device, size_t count);
+/* d2h without the wait: ordered on the stream, dst_host (page-locked) is valid after the
+ * next katsu_cuda_sync.  Lets a caller keep several contexts (streams) of one device busy,
+ * e.g. copying one batch chunk out while the next one computes. */
+int32_t katsu_cuda_d2h_async(katsu_cuda_ctx *ctx, float *dst_host, const float *src_device, size_t count);
 int32_t katsu_cuda_d2d(katsu_cuda_ctx *ctx, float *dst_device, const float *src_device, size_t count);
 /* Page-locked host staging buffers so h2d/d2h run at full PCIe rate. */
 int32_t katsu_cuda_host_alloc(katsu_cuda_ctx *ctx, size_t count, float **out_ptr);

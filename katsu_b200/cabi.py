@@ -41,6 +41,7 @@ SIGNATURES = {
     "katsu_cuda_zero": [_ctx, _ptr, _sz],
     "katsu_cuda_h2d": [_ctx, _ptr, ctypes.c_void_p, _sz],
     "katsu_cuda_d2h": [_ctx, ctypes.c_void_p, _ptr, _sz],
+    "katsu_cuda_d2h_async": [_ctx, ctypes.c_void_p, _ptr, _sz],
     "katsu_cuda_d2d": [_ctx, _ptr, _ptr, _sz],
     "katsu_cuda_host_alloc": [_ctx, _sz, ctypes.POINTER(ctypes.c_void_p)],
     "katsu_cuda_host_free": [_ctx, ctypes.c_void_p],
@@ -162,6 +163,11 @@ class Context:
     def d2h(self, array: np.ndarray, ptr: int) -> None:
         assert array.dtype == np.float32 and array.flags["C_CONTIGUOUS"]
         self.call("katsu_cuda_d2h", array.ctypes.data, ptr, array.size)
+
+    def d2h_async(self, array: np.ndarray, ptr: int) -> None:
+        """Stream-ordered copy into a page-locked array; valid after sync()."""
+        assert array.dtype == np.float32 and array.flags["C_CONTIGUOUS"]
+        self.call("katsu_cuda_d2h_async", array.ctypes.data, ptr, array.size)
 
     def pinned(self, count: int) -> np.ndarray:
         """A page-locked f32 numpy array of `count` elements (freed with free_pinned)."""

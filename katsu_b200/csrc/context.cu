@@ -185,6 +185,14 @@ extern "C" int32_t katsu_cuda_d2h(katsu_cuda_ctx *ctx, float *dst_host, const fl
     return KATSU_OK;
 }
 
+extern "C" int32_t katsu_cuda_d2h_async(katsu_cuda_ctx *ctx, float *dst_host, const float *src_device, size_t count) {
+    KATSU_TRY(katsu_bind(ctx));
+    if (count == 0) return KATSU_OK;
+    KATSU_REQUIRE(dst_host != nullptr && src_device != nullptr, "null buffer");
+    KATSU_CUDA_TRY(cudaMemcpyAsync(dst_host, src_device, count * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    return KATSU_OK;
+}
+
 extern "C" int32_t katsu_cuda_d2d(katsu_cuda_ctx *ctx, float *dst_device, const float *src_device, size_t count) {
     KATSU_TRY(katsu_bind(ctx));
     if (count == 0) return KATSU_OK;

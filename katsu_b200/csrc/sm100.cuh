@@ -121,7 +121,7 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// ---- TMA (tiled mode, no multicast) ------------------------------------------
+// ---- TMA (tiled mode; every block issues its own loads) -------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
