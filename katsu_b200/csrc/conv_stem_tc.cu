@@ -68,10 +68,13 @@ __device__ __forceinline__ void store_chunk(unsigned char *tile, int row, int ch
 
 constexpr int A_TILE = 128 * 128;  // bytes: 128 rows x 128 B
 
-// Warp roles of the forward kernel (18 warps):
-//   0-3, 4-7   two epilogue groups (alternate tiles; warp % 4 selects the TMEM lane quarter)
-//   8-11, 12-15 two builder groups (alternate tiles)
-//   16         MMA issue (one thread)      17  TMA loads of the x halo tiles (one thread)
+// Warp roles of the forward kernel, GROUPS = 1 or 2 (10 or 18 warps):
+//   [0, 4G)      G epilogue groups (alternate tiles; warp % 4 selects the TMEM lane quarter)
+//   [4G, 8G)     G builder groups (alternate tiles)
+//   8G           MMA issue (one thread)      8G+1  TMA loads of the x halo tiles (one thread)
+// GROUPS = 1 runs two blocks per SM (256 TMEM columns each) so that one block's hand-off
+// latencies are covered by the other block's work; GROUPS = 2 is the single-block form for
+// channel counts whose accumulators need more than 256 columns.
 // Per-tile hand-offs cost several hundred cycles each, so every resource is buffered deeper
 // than the role count: AS stages of A, NB accumulators, XS x tiles, one staging buffer per
 // epilogue group.  A lives in tensor memory, not shared memory: with A in shared memory the
@@ -79,15 +82,16 @@ constexpr int A_TILE = 128 * 128;  // bytes: 128 rows x 128 B
 // reads, B reads, x reads, output staging) and was bound by that pipe; the tcgen05 form
 // with A in TMEM leaves ~810.
 //   TMEM columns: [NB accumulators x np][AS stages x {32 hi, 32 lo}]
-constexpr int FWD_THREADS = 576;
 constexpr int XS = 6;   // x halo tiles in flight
 
-template <int CIN>
-__global__ void __launch_bounds__(FWD_THREADS, 1)
+template <int CIN, int GROUPS>
+__global__ void __launch_bounds__((8 * GROUPS + 2) * 32, GROUPS == 1 ? 2 : 1)
 stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __grid_constant__ CUtensorMap map_x,
                    StemDims d) {
     constexpr int TAPS = CIN * 9;
     constexpr int XT = (CIN * 6 * 40 + 31) / 32 * 32;  // x stage pitch in floats: keeps stages 128-byte aligned
+    constexpr int FWD_THREADS = (8 * GROUPS + 2) * 32;
+    constexpr int MMA_WARP = 8 * GROUPS, TMA_WARP = 8 * GROUPS + 1;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     // dynamic layout: B hi | B lo | output staging x 2 groups
@@ -121,7 +125,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
         }
         mbar_init_fence();
     }
-    if (warp == 16) {
+    if (warp == MMA_WARP) {
         tmem_alloc(&tmem_slot, tmem_cols);
         tmem_relinquish();
     }
@@ -145,13 +149,13 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
     const uint32_t tmem_base = tmem_slot;
     const size_t plane = size_t(d.h) * d.w;
 
-    if (warp >= 8 && warp < 16) {
+    if (warp >= 4 * GROUPS && warp < 8 * GROUPS) {
         // ---- builders: one pixel (one A row) per thread, window read from the x halo tile ----
-        const int group = (warp - 8) >> 2;
+        const int group = (warp - 4 * GROUPS) >> 2;
         const int r = (warp & 3) * 32 + lane;
         const int win = (r >> 5) * 40 + (r & 31) + 3;  // window origin (ky = kx = 0) inside a channel's 6x40 tile
         PROF_DECL
-        for (int it = group; it < my_tiles; it += 2) {
+        for (int it = group; it < my_tiles; it += GROUPS) {
             const int s = it % AS, xs = it % XS;
             if (!mbar_wait_warp(&x_full[xs], (it / XS) & 1, d.status, 45)) break;
             PROF_MARK(0)
@@ -187,7 +191,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
             PROF_MARK(3)
         }
         if (r == 0 && group == 0) PROF_DUMP(0)
-    } else if (warp == 17 && lane == 0) {
+    } else if (warp == TMA_WARP && lane == 0) {
         // ---- TMA loads of the x halo tiles ----
         for (int it = 0; it < my_tiles; ++it) {
             const int s = it % XS;
@@ -197,7 +201,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
             mbar_arrive_expect_tx(&x_full[s], CIN * 6 * 40 * 4);
             tma_load_4d(x_tiles[s], &map_x, &x_full[s], (tt % d.tiles_x) * 32 - 4, (tt / d.tiles_x) * 4 - 1, 0, img);
         }
-    } else if (warp == 16 && lane == 0) {
+    } else if (warp == MMA_WARP && lane == 0) {
         // ---- MMA issue: descriptors are precomputed, this one thread is on the critical path ----
         const uint32_t idesc = idesc_tf32(128, d.np, false, false);
         uint64_t db_hi[4], db_lo[4];
@@ -231,7 +235,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
             PROF_MARK(2)
         }
         PROF_DUMP(1)
-    } else if (warp < 8) {
+    } else if (warp < 4 * GROUPS) {
         // ---- epilogue: TMEM -> registers (thread = pixel) -> shared staging [oc][4 rows][32 px]
         // -> global with 128-bit stores (a warp writes the four 128-byte row segments of one
         // channel's tile per instruction), 64 channels per staging pass ----
@@ -241,7 +245,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
         const int bar_id = 1 + group;
         float *stage = out_stages + group * (64 * 128);
         PROF_DECL
-        for (int it = group; it < my_tiles; it += 2) {
+        for (int it = group; it < my_tiles; it += GROUPS) {
             const int b = it % NB;
             if (!mbar_wait_warp(&acc_full[b], (it / NB) & 1, d.status, 44)) break;
             tc_fence_after_sync();
@@ -283,7 +287,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 16) tmem_dealloc(tmem_base, tmem_cols);
+    if (warp == MMA_WARP) tmem_dealloc(tmem_base, tmem_cols);
 }
 
 bool stem_tc_shape(const katsu_cuda_ctx *ctx, size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
@@ -295,8 +299,8 @@ bool stem_tc_shape(const katsu_cuda_ctx *ctx, size_t n, size_t c, size_t h, size
     return n * katsu_div_up(h, 4) * katsu_div_up(wd, 32) <= 0x7fffffffu;
 }
 
-template <int CIN>
-int32_t fwd_launch(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y, StemDims d) {
+template <int CIN, int GROUPS>
+int32_t fwd_launch_groups(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y, StemDims d) {
     // x as [N][C][H][W] with a box of one halo tile: 40 columns x 6 rows x all channels
     CUtensorMap map_x;
     {
@@ -306,18 +310,30 @@ int32_t fwd_launch(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y
         if (!katsu_make_tensor_map(&map_x, x, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
             return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (stem forward x)");
     }
-    const size_t smem = 2 * size_t(d.np) * 128 + 2 * 64 * 512 + 1024;  // filters, two staging buffers, alignment slack
+    // filters, one staging buffer per epilogue group, alignment slack.  The two-blocks-per-SM
+    // form asks for at least 90 KiB so that a third block (which could not get TMEM columns)
+    // is never co-resident.
+    size_t smem = 2 * size_t(d.np) * 128 + size_t(GROUPS) * 64 * 512 + 1024;
+    if (GROUPS == 1 && smem < 90 * 1024) smem = 90 * 1024;
     // tensor memory: accumulators first, then the A stages (64 columns each)
-    d.acc_buffers = 4 * d.np + 2 * 64 <= 512 ? 4 : 2;
-    d.a_stages = (512 - d.acc_buffers * d.np) / 64;
+    const int cols = GROUPS == 1 ? 256 : 512;
+    d.acc_buffers = (4 * d.np + 2 * 64 <= cols) ? 4 : 2;
+    d.a_stages = (cols - d.acc_buffers * d.np) / 64;
     if (d.a_stages > 3) d.a_stages = 3;
-    auto kernel = stem_fwd_tc_kernel<CIN>;
+    auto kernel = stem_fwd_tc_kernel<CIN, GROUPS>;
     KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const size_t total_tiles = size_t(d.n) * d.tiles_x * d.tiles_y;
-    size_t grid = ctx->num_sms;
+    size_t grid = size_t(ctx->num_sms) * (GROUPS == 1 ? 2 : 1);
     if (grid > total_tiles) grid = total_tiles;
-    KATSU_LAUNCH(ctx, kernel, (unsigned)grid, FWD_THREADS, smem, w, y, map_x, d);
+    KATSU_LAUNCH(ctx, kernel, (unsigned)grid, (8 * GROUPS + 2) * 32, smem, w, y, map_x, d);
     return KATSU_OK;
+}
+
+template <int CIN>
+int32_t fwd_launch(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y, StemDims d) {
+    // two accumulators + two A stages in 256 TMEM columns: np <= 64
+    if (d.np <= 64) return fwd_launch_groups<CIN, 1>(ctx, x, w, y, d);
+    return fwd_launch_groups<CIN, 2>(ctx, x, w, y, d);
 }
 
 }  // namespace
