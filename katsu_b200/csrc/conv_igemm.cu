@@ -621,7 +621,13 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr
     }
     const size_t total_groups = n * p.groups_x * p.groups_y;
     const size_t out_tiles = katsu_div_up(k, (size_t)BM) * katsu_div_up(c, (size_t)BN) * taps;
+    // Split the pixel range so that the grid fills whole waves of the GPU: the smallest split
+    // count (at least two blocks' worth of work per SM) whose last wave is >= 95 % full.
     size_t splits = katsu_div_up(size_t(ctx->num_sms) * 2, out_tiles);
+    for (size_t cand = splits; cand < splits + size_t(ctx->num_sms); ++cand) {
+        const size_t blocks = out_tiles * cand, waves = katsu_div_up(blocks, (size_t)ctx->num_sms);
+        if (blocks * 100 >= waves * ctx->num_sms * 95) { splits = cand; break; }
+    }
     if (splits > total_groups) splits = total_groups;
     if (splits < 1) splits = 1;
     p.groups_per_split = (int)katsu_div_up(total_groups, splits);
