@@ -66,7 +66,11 @@ int32_t katsu_cuda_stream(katsu_cuda_ctx *ctx, void **out_stream);
 
 /* ---- memory ------------------------------------------------------------ */
 /* Zero-filled device buffer of `count` floats: zeros_buffer,
- * crates/katsu-core/src/tensor.rs:120-125.  count == 0 yields a null pointer. */
+ * crates/katsu-core/src/tensor.rs:120-125.  count == 0 yields a null pointer.
+ * Allocation and release are ordered on the context's stream and served from a
+ * cached pool, so a step that frees and re-allocates its buffers does not
+ * synchronise the device.  A buffer must be freed through a context whose
+ * stream has seen (or been synchronised with) its last use. */
 int32_t katsu_cuda_alloc(katsu_cuda_ctx *ctx, size_t count, float **out_ptr);
 int32_t katsu_cuda_free(katsu_cuda_ctx *ctx, float *ptr);
 int32_t katsu_cuda_zero(katsu_cuda_ctx *ctx, float *dst, size_t count);

@@ -73,6 +73,18 @@ extern "C" int32_t katsu_cuda_init(int32_t device, katsu_cuda_ctx **out_ctx) {
     ctx->device = device;
     ctx->num_sms = prop.multiProcessorCount;
     ctx->precision = KATSU_MODE_3XTF32;
+    // katsu_cuda_alloc / katsu_cuda_free are stream-ordered (cudaMallocAsync on the device's
+    // default pool).  Keep freed blocks cached: an autograd step allocates and frees the same
+    // few hundred MB of adjoint buffers every time, and cudaMalloc / cudaFree each cost a
+    // device-wide synchronisation (measured: 34 ms -> a few ms per step of the small CNN).
+    {
+        cudaMemPool_t pool;
+        if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
+            unsigned long long keep = ~0ull;
+            cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+        }
+        cudaGetLastError();
+    }
     err = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (err == cudaSuccess) err = cudaMalloc(&ctx->status, sizeof(int));
     if (err == cudaSuccess) err = cudaMemsetAsync(ctx->status, 0, sizeof(int), ctx->stream);
@@ -134,15 +146,15 @@ extern "C" int32_t katsu_cuda_alloc(katsu_cuda_ctx *ctx, size_t count, float **o
     if (count > SIZE_MAX / sizeof(float))
         return katsu_set_error(KATSU_ERR_ALLOC, "allocation of %zu floats overflows", count);
     float *p = nullptr;
-    cudaError_t err = cudaMalloc(&p, count * sizeof(float));
+    cudaError_t err = cudaMallocAsync(&p, count * sizeof(float), ctx->stream);
     if (err != cudaSuccess) {
         cudaGetLastError();
-        return katsu_set_error(KATSU_ERR_ALLOC, "cudaMalloc(%zu bytes): %s", count * sizeof(float),
+        return katsu_set_error(KATSU_ERR_ALLOC, "cudaMallocAsync(%zu bytes): %s", count * sizeof(float),
                                cudaGetErrorString(err));
     }
     err = cudaMemsetAsync(p, 0, count * sizeof(float), ctx->stream);
     if (err != cudaSuccess) {
-        cudaFree(p);
+        cudaFreeAsync(p, ctx->stream);
         return katsu_set_error(KATSU_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(err));
     }
     *out_ptr = p;
@@ -152,8 +164,9 @@ extern "C" int32_t katsu_cuda_alloc(katsu_cuda_ctx *ctx, size_t count, float **o
 extern "C" int32_t katsu_cuda_free(katsu_cuda_ctx *ctx, float *ptr) {
     KATSU_TRY(katsu_bind(ctx));
     if (ptr == nullptr) return KATSU_OK;
-    // cudaFree waits for work that may still use the block.
-    KATSU_CUDA_TRY(cudaFree(ptr));
+    // Stream-ordered: work already queued on this context's stream may still use the block;
+    // work queued on another context must have been synchronised by the caller.
+    KATSU_CUDA_TRY(cudaFreeAsync(ptr, ctx->stream));
     return KATSU_OK;
 }
 
