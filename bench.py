@@ -386,18 +386,134 @@ def run_ours(args):
     return 0
 
 
+def run_small_cnn(args):
+    """BASELINE config 5: conv 3->32 s1 p1, conv 32->64 s2 p1, reshape, matmul [N,65536]@[65536,10], add a
+    constant, loss = sum(out*out), loss.backward() -- the whole autograd graph on the device through the
+    katsu_b200 surface (the C++ host mirror), batch sharded over the ranks, the three weight gradients
+    summed with one all-reduce of a flat bucket."""
+    rank, local_rank, world = dist_env()
+    import katsu_b200 as K
+    from katsu_b200 import cabi, dp
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
+    K.set_device(local_rank)
+    total = args.batch or workloads.CNN["batch"]
+    first, batch = dp.shard(total, rank, world)
+    c1 = workloads.CONV["cnn_conv1"].with_batch(total)
+    c2 = workloads.CONV["cnn_conv2"].with_batch(total)
+    x, w1 = workloads.conv_inputs(c1, first, batch)
+    _, w2 = workloads.conv_inputs(c2, 0, 1)
+    fc_in, fc_out = workloads.CNN["fc_in"], workloads.CNN["fc_out"]
+    tx = K.Tensor(x, [batch, c1.c, c1.h, c1.w]).to_device()
+    tw1 = K.Tensor(w1, c1.w_shape).to_device()
+    tw2 = K.Tensor(w2, c2.w_shape).to_device()
+    twfc = K.Tensor(workloads.cnn_fc_weights(), [fc_in, fc_out]).to_device()
+    tconst = K.Tensor(workloads.cnn_constant(first, batch), [batch, fc_out]).to_device()
+    params = {"w1": tw1, "w2": tw2, "wfc": twfc}
+    raw = cabi.load()
+    handle = K.context()
+
+    def call(name, *a):
+        cabi.check(getattr(raw, name)(handle, *a))
+
+    import ctypes
+
+    bucket_ptr, offsets, cursor = None, {}, 0
+    for name, t in params.items():
+        offsets[name] = cursor
+        cursor += -(-t.numel() // 64) * 64
+    if world > 1:
+        out = ctypes.c_void_p()
+        call("katsu_cuda_alloc", cursor, ctypes.byref(out))
+        bucket_ptr = out.value
+        ident = [None]
+        if rank == 0:
+            buf = (ctypes.c_uint8 * cabi.COMM_ID_BYTES)()
+            cabi.check(raw.katsu_cuda_comm_unique_id(buf))
+            ident[0] = bytes(buf)
+        dist.broadcast_object_list(ident, src=0)
+        call("katsu_cuda_comm_init", (ctypes.c_uint8 * cabi.COMM_ID_BYTES).from_buffer_copy(ident[0]), world, rank)
+
+    def step():
+        conv1 = K.Conv2D.from_weights(tw1, 1, 1)
+        conv2 = K.Conv2D.from_weights(tw2, 2, 1)
+        h2 = conv2.forward(conv1.forward(tx))
+        out = h2.reshape([batch, fc_in]).matmul(twfc).add(tconst)
+        loss = out.mul(out).sum()
+        loss.backward()
+        if world > 1:
+            for name, t in params.items():
+                call("katsu_cuda_d2d", bucket_ptr + 4 * offsets[name], t.device_grad(), t.numel())
+            call("katsu_cuda_allreduce_sum", bucket_ptr, cursor)
+        for t in (tx, tw1, tw2, twfc, tconst):
+            t.zero_grad()
+        return loss
+
+    def barrier():
+        K.synchronize()
+        if dist is not None:
+            import torch
+
+            dist.barrier(device_ids=[local_rank])
+            torch.cuda.synchronize()
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        step()
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            loss = step()
+        K.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    barrier()
+    loss_value = float(loss.data()[0])
+    if dist is not None:
+        import torch
+
+        t = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    if rank == 0:
+        flops = 6 * (c1.macs + c2.macs + total * fc_in * fc_out)
+        print(json.dumps({
+            "metric": "small_cnn_fwd_bwd_images_per_s", "value": total / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "small_cnn", "global_batch": total, "images_per_gpu": batch,
+                       "graph": "conv3->32 s1p1, conv32->64 s2p1, reshape, matmul [N,65536]x[65536,10], add, sum(out*out), backward",
+                       "timing": "host wall clock around whole graph steps, device synchronised at both ends"},
+            "tflops": flops / (ms * 1e-3) / 1e12, "loss_rank0": loss_value, "clocks": clocks.summary()}), flush=True)
+    if dist is not None:
+        call("katsu_cuda_comm_destroy")
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", default="stem_256x3x224", choices=sorted(workloads.CONV))
+    ap.add_argument("--workload", default="stem_256x3x224", choices=sorted(workloads.CONV) + ["small_cnn"])
     ap.add_argument("--scaling", choices=["strong", "weak"], default="strong")
     ap.add_argument("--cpu-sample", type=int, default=32, help="images in the single-thread CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (small profiling cases)")
     args = ap.parse_args()
+    if args.workload == "small_cnn":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference arm times the conv workloads only"}))
+            return 0
+        return run_small_cnn(args)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)

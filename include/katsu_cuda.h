@@ -161,6 +161,13 @@ int32_t katsu_cuda_comm_destroy(katsu_cuda_ctx *ctx);
 /* In-place sum over all ranks of a flat gradient bucket, on the context's stream. */
 int32_t katsu_cuda_allreduce_sum(katsu_cuda_ctx *ctx, float *buf, size_t count);
 
+/* ---- diagnostics (no counterpart in the reference) ------------------------ */
+/* Launches one block that waits, for at most `cycles` SM clocks (1e3..2e8), on a barrier
+ * nothing signals.  The wait gives up and the kernel returns; the next katsu_cuda_sync
+ * then returns KATSU_ERR_TIMEOUT once and the context remains usable.  Exercises the bounded-
+ * wait path of the pipelined kernels without faulting or hanging the device. */
+int32_t katsu_cuda_selftest_wait_timeout(katsu_cuda_ctx *ctx, uint64_t cycles);
+
 /* ---- timing on the context's stream ------------------------------------ */
 int32_t katsu_cuda_event_create(katsu_cuda_ctx *ctx, katsu_cuda_event **out_event);
 int32_t katsu_cuda_event_record(katsu_cuda_ctx *ctx, katsu_cuda_event *event);

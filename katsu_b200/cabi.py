@@ -66,6 +66,7 @@ SIGNATURES = {
     "katsu_cuda_event_elapsed_ms": [_ctx, ctypes.c_void_p, ctypes.c_void_p, _c_float_p],
     "katsu_cuda_event_destroy": [_ctx, ctypes.c_void_p],
     "katsu_cuda_flush_l2": [_ctx],
+    "katsu_cuda_selftest_wait_timeout": [_ctx, ctypes.c_uint64],
 }
 
 _lib = None

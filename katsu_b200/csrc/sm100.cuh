@@ -92,18 +92,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 constexpr uint32_t kWaitPolls = 1u << 24;
 constexpr long long kWaitCycles = 2000000000ll;
 
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status, int code) {
+__device__ __forceinline__ bool mbar_wait_budget(uint64_t *bar, uint32_t parity, int *status, int code,
+                                                 long long cycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     for (uint32_t i = 0; i < kWaitPolls; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-#ifdef KATSU_WAIT_SLEEP
-        __nanosleep(KATSU_WAIT_SLEEP);
-#endif
-        if ((i & 63u) == 63u && clock64() - start > kWaitCycles) break;
+        if ((i & 63u) == 63u && clock64() - start > cycles) break;
     }
     if (status != nullptr) atomicCAS(status, 0, code);
     return false;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status, int code) {
+    return mbar_wait_budget(bar, parity, status, code, kWaitCycles);
 }
 
 // Whole-warp wait: lane 0 polls, the warp then reconverges.  32 lanes polling one

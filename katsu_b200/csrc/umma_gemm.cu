@@ -271,6 +271,28 @@ int32_t launch(katsu_cuda_ctx *ctx, const float *a, const float *b, float *c, si
 
 }  // namespace
 
+// Diagnostic: one block waits, with a budget of `cycles` SM clocks, on an mbarrier that
+// nothing ever arrives on.  The wait gives up, records code 99 in the context's status word
+// and the kernel returns normally; the next katsu_cuda_sync reports KATSU_ERR_TIMEOUT and
+// the context stays usable.  This is the path every pipeline wait in the tensor-core
+// kernels takes if a hand-off is ever missed.
+__global__ void wait_timeout_probe_kernel(int *status, long long cycles) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    mbar_wait_budget(&bar, 0, status, 99, cycles);
+}
+
+extern "C" int32_t katsu_cuda_selftest_wait_timeout(katsu_cuda_ctx *ctx, uint64_t cycles) {
+    KATSU_TRY(katsu_bind(ctx));
+    KATSU_REQUIRE(cycles >= 1000 && cycles <= 200000000ull, "cycle budget must be between 1e3 and 2e8");
+    KATSU_LAUNCH(ctx, wait_timeout_probe_kernel, 1, 32, 0, ctx->status, (long long)cycles);
+    return KATSU_OK;
+}
+
 // C[M,N] (+)= A * B on the tensor cores.  a_mn / b_mn: operand stored with its
 // M (resp. N) index contiguous instead of K.  *handled = 0 when the shape does
 // not meet TMA's alignment rules or is too small to be worth a 128x128 tile;
