@@ -132,6 +132,11 @@ int32_t katsu_conv_stem_tc_fwd(katsu_cuda_ctx *ctx, const float *x, const float 
                                size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
                                size_t stride, size_t pad, int *handled);
 
+// dX of the same shape family on the tensor cores (conv_stem_tc_bwd.cu); *handled = 0 in FP32
+// mode or when TMA cannot describe the tensors.
+int32_t katsu_conv_stem_tc_dx(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx, size_t n, size_t c,
+                              size_t h, size_t wd, size_t k, int accumulate, int *handled);
+
 // TMA-fed dX stencil (conv_stencil_tma.cu); *handled = 0 when TMA cannot describe g.
 int32_t katsu_stencil_dx_tma(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx, size_t n, size_t c,
                              size_t h, size_t wd, size_t k, int accumulate, int *handled);

@@ -31,20 +31,9 @@
 
 using namespace sm100;
 
-// Per-role cycle accounting for tuning builds (-DKATSU_ROLE_PROF); compiled out otherwise.
-#ifdef KATSU_ROLE_PROF
-__device__ long long g_katsu_role_prof[256 * 16];
-extern "C" int katsu_debug_role_prof(long long *out) {
-    return (int)cudaMemcpyFromSymbol(out, g_katsu_role_prof, sizeof(long long) * 256 * 16);
-}
-#define PROF_DECL long long pt_[4] = {0, 0, 0, 0}, pc_ = clock64();
-#define PROF_MARK(i) { const long long n_ = clock64(); pt_[i] += n_ - pc_; pc_ = n_; }
-#define PROF_DUMP(slot) { for (int q_ = 0; q_ < 4; ++q_) g_katsu_role_prof[blockIdx.x * 16 + (slot) * 4 + q_] = pt_[q_]; }
-#else
-#define PROF_DECL
-#define PROF_MARK(i) {}
-#define PROF_DUMP(slot) {}
-#endif
+#define KATSU_PROF_ARRAY g_katsu_role_prof
+#define KATSU_PROF_READER katsu_debug_role_prof
+#include "role_prof.cuh"
 
 namespace {
 
@@ -201,8 +190,12 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
             mbar_arrive_expect_tx(&x_full[s], CIN * 6 * 40 * 4);
             tma_load_4d(x_tiles[s], &map_x, &x_full[s], (tt % d.tiles_x) * 32 - 4, (tt / d.tiles_x) * 4 - 1, 0, img);
         }
-    } else if (warp == MMA_WARP && lane == 0) {
-        // ---- MMA issue: descriptors are precomputed, this one thread is on the critical path ----
+    } else if (warp == MMA_WARP) {
+        // ---- MMA issue: descriptors are precomputed, this role is on the critical path.  The
+        // whole warp runs the loop and the thread chosen by elect.sync issues; with warp-uniform
+        // control flow the operands stay in uniform registers (measured: one small-N MMA per
+        // ~22 cycles, against 44 behind a lane == 0 branch). ----
+        const bool issue = elect_one();
         const uint32_t idesc = idesc_tf32(128, d.np, false, false);
         uint64_t db_hi[4], db_lo[4];
 #pragma unroll
@@ -213,28 +206,33 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
         PROF_DECL
         for (int it = 0; it < my_tiles; ++it) {
             const int s = it % AS, b = it % NB;
-            if (!mbar_wait(&full[s], (it / AS) & 1, d.status, 42)) break;
+            if (!mbar_wait_warp(&full[s], (it / AS) & 1, d.status, 42)) break;
             PROF_MARK(0)
-            if (it >= NB && !mbar_wait(&acc_empty[b], ((it / NB) - 1) & 1, d.status, 43)) break;
+            if (it >= NB && !mbar_wait_warp(&acc_empty[b], ((it / NB) - 1) & 1, d.status, 43)) break;
             PROF_MARK(1)
             tc_fence_after_sync();
             const uint32_t acc = tmem_base + uint32_t(b) * d.np;
             const uint32_t a_hi = tmem_base + a_col0 + uint32_t(s) * 64, a_lo = a_hi + 32;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                if (d.three_pass) {
-                    mma_tf32_ts(acc, a_lo + 8 * j, db_hi[j], idesc, j != 0);
-                    mma_tf32_ts(acc, a_hi + 8 * j, db_lo[j], idesc, true);
-                    mma_tf32_ts(acc, a_hi + 8 * j, db_hi[j], idesc, true);
-                } else {
-                    mma_tf32_ts(acc, a_hi + 8 * j, db_hi[j], idesc, j != 0);
+                if (issue) {
+                    if (d.three_pass) {
+                        mma_tf32_ts(acc, a_lo + 8 * j, db_hi[j], idesc, j != 0);
+                        mma_tf32_ts(acc, a_hi + 8 * j, db_lo[j], idesc, true);
+                        mma_tf32_ts(acc, a_hi + 8 * j, db_hi[j], idesc, true);
+                    } else {
+                        mma_tf32_ts(acc, a_hi + 8 * j, db_hi[j], idesc, j != 0);
+                    }
                 }
             }
-            mma_commit(&empty[s]);
-            mma_commit(&acc_full[b]);
+            if (issue) {
+                mma_commit(&empty[s]);
+                mma_commit(&acc_full[b]);
+            }
+            __syncwarp();
             PROF_MARK(2)
         }
-        PROF_DUMP(1)
+        if (lane == 0) PROF_DUMP(1)
     } else if (warp < 4 * GROUPS) {
         // ---- epilogue: TMEM -> registers (thread = pixel) -> shared staging [oc][4 rows][32 px]
         // -> global with 128-bit stores (a warp writes the four 128-byte row segments of one

@@ -1,0 +1,345 @@
+// Backward of the low-channel (C_in <= 3) 3x3 stride-1 pad-1 convolution on the tensor cores.
+//
+// Reference loops: backward_buffers (crates/katsu-core/src/conv2d.rs:269-292), i.e. for every
+// visited (n, oc, oy, ox, ic, ky, kx): dX[n,ic,iy,ix] += g[n,oc,oy,ox] * W[oc,ic,ky,kx] and
+// dW[oc,ic,ky,kx] += g[n,oc,oy,ox] * x[n,ic,iy,ix].
+//
+// On the FP32 pipe each of the two needs 27 * C_out multiply-adds per pixel, more time than
+// reading g from HBM once.  As contractions over oc (dX) and over pixels (dW) they are a few
+// hundred tensor-pipe cycles per 128 pixels and the kernels become bound by the read of g.
+//
+// dX:  Z[pixel, tap] = sum_oc g[oc, pixel] * W[oc, tap]         (a GEMM, K = C_out, N = 27 -> 32)
+//      dX[c, iy, ix] = sum_{ky,kx} Z[(iy + 1 - ky, ix + 1 - kx), (c, ky, kx)]   (col2im)
+//   A = g^T, 128 pixels x 16 oc per stage, held in TENSOR MEMORY (lane = pixel, column = oc) as
+//       hi = trunc_tf32(v) and lo = v - hi, written by builder warps from the g tile TMA
+//       dropped into shared memory ([16 oc][16 rows][36 columns], start column rounded down
+//       to a 16-byte boundary, out-of-image cells arrive as zeros).
+//   B = W as [tap][oc], K-major 128-byte-swizzled rows, built once per block (hi and lo).
+//   D = four 128 x 32 accumulators per tile (a 16 x 32 pixel region of g), double buffered.
+//   Every Z value is used exactly once, so the col2im is a gather through shared memory:
+//   Z leaves TMEM as [tap][pixel] planes, each output pixel adds its nine (ky, kx) terms per
+//   channel in a fixed order, and the 14 x 28 output tile goes out with one TMA store.
+//   The region overlaps its neighbours by one pixel on each side (recomputed, not exchanged),
+//   so no two blocks ever add into the same dX element and results are bit-reproducible.
+//   Two warps issue MMAs (two M-tiles each): one thread sustains one small-N MMA per ~44
+//   cycles, two reach the tensor pipe's rate (measured).
+#include "common.cuh"
+#include <string.h>
+
+#include "sm100.cuh"
+
+using namespace sm100;
+
+#define KATSU_PROF_ARRAY g_katsu_role_prof_bwd
+#define KATSU_PROF_READER katsu_debug_role_prof_bwd
+#include "role_prof.cuh"
+
+namespace {
+
+__device__ __forceinline__ float tf32_hi(float v) { return __uint_as_float(__float_as_uint(v) & 0xFFFFE000u); }
+
+__device__ __forceinline__ void store_chunk(unsigned char *tile, int row, int chunk, float4 v) {
+    st_shared_v4(tile + row * 128 + ((chunk ^ (row & 7)) << 4), v);
+}
+
+struct StemDxDims {
+    int n, k, h, w;
+    int tiles_x, tiles_y;   // 28-column, 14-row output tiles
+    int chunks;             // 16-oc chunks of g per tile
+    int kblocks;            // 32-oc blocks of the filter operand
+    int three_pass;
+    int accumulate;
+    int *status;
+};
+
+constexpr int DX_TW = 28, DX_TH = 14;          // output tile
+constexpr int DX_RW = 32, DX_RH = 16;          // g region that is multiplied (one halo pixel each side, padded)
+constexpr int DX_GW = 36;                      // g columns TMA loads per row (region starts at column 3)
+constexpr int DX_OC = 16;                      // oc per chunk
+constexpr int DX_GSTAGE = DX_OC * DX_RH * DX_GW;  // floats per g stage
+constexpr int DX_GS = 4;                       // g stages
+constexpr int DX_ZP = DX_RW * DX_RH;           // pixels per Z plane
+constexpr int DX_THREADS = 15 * 32;
+
+// Warp roles: 0-3 epilogue (TMEM lane quarter = warp), 4-11 builders (quarter = warp & 3,
+// M-tiles {0,1} for warps 4-7 and {2,3} for warps 8-11), 12-13 MMA issue (M-tiles {0,1} and
+// {2,3}), 14 TMA loads of g.
+// TMEM columns: [2 D buffers x 4 M-tiles x 32][2 A stages x 4 M-tiles x {16 hi, 16 lo}] = 512.
+template <int CIN>
+__global__ void __launch_bounds__(DX_THREADS, 1)
+stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant__ CUtensorMap map_g,
+                  const __grid_constant__ CUtensorMap map_dx, StemDxDims d) {
+    constexpr int TAPS = CIN * 9;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // dynamic layout: B hi | B lo | g stages | Z planes | output tile
+    unsigned char *b_hi = smem;
+    unsigned char *b_lo = b_hi + d.kblocks * 4096;
+    float *g_stages = reinterpret_cast<float *>(b_lo + d.kblocks * 4096);
+    float *zs = g_stages + DX_GS * DX_GSTAGE;
+    float *outs = zs + TAPS * DX_ZP;
+    __shared__ uint64_t g_full[DX_GS], g_empty[DX_GS], a_full[2], a_empty[2], d_full[2], d_empty[2];
+    __shared__ uint32_t tmem_slot;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tiles_per_img = d.tiles_x * d.tiles_y;
+    const int total_tiles = d.n * tiles_per_img;
+    const int my_tiles = (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int NCH = d.chunks;
+
+    if (tid == 0) {
+        for (int s = 0; s < DX_GS; ++s) {
+            mbar_init(&g_full[s], 1);
+            mbar_init(&g_empty[s], 8);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&a_full[s], 256);
+            mbar_init(&a_empty[s], 2);
+            mbar_init(&d_full[s], 2);
+            mbar_init(&d_empty[s], 128);
+        }
+        mbar_init_fence();
+    }
+    if (warp == 12) {
+        tmem_alloc(&tmem_slot, 512);
+        tmem_relinquish();
+    }
+    // filters -> B tiles: row = tap, 32 oc per 128-byte row, one tile of 32 rows per oc block
+    for (int i = tid; i < d.kblocks * 32 * 8; i += DX_THREADS) {
+        const int blk = i >> 8, t = (i >> 3) & 31, j = i & 7;
+        float v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int oc = blk * 32 + 4 * j + q;
+            v[q] = (oc < d.k && t < TAPS) ? __ldg(w + size_t(oc) * TAPS + t) : 0.f;
+        }
+        const float4 hi = make_float4(tf32_hi(v[0]), tf32_hi(v[1]), tf32_hi(v[2]), tf32_hi(v[3]));
+        store_chunk(b_hi + blk * 4096, t, j, hi);
+        store_chunk(b_lo + blk * 4096, t, j, make_float4(v[0] - hi.x, v[1] - hi.y, v[2] - hi.z, v[3] - hi.w));
+    }
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_slot;
+    constexpr uint32_t A_COL0 = 256;
+
+    if (warp >= 4 && warp < 12) {
+        // ---- builders: thread = one pixel of two M-tiles; 16 oc per chunk -> TMEM A (hi | lo) ----
+        const int quarter = warp & 3, half = (warp - 4) >> 2;
+        PROF_DECL
+        for (int it = 0; it < my_tiles; ++it) {
+            bool ok = true;
+            for (int q = 0; q < NCH; ++q) {
+                const int cc = it * NCH + q, gs = cc % DX_GS, as = cc & 1;
+                if (!mbar_wait_warp(&g_full[gs], (cc / DX_GS) & 1, d.status, 61)) { ok = false; break; }
+                PROF_MARK(0)
+                const float *st = g_stages + gs * DX_GSTAGE + 3 + lane;
+                float v[2][32];
+#pragma unroll
+                for (int m = 0; m < 2; ++m) {
+                    const int row = 4 * (2 * half + m) + quarter;
+#pragma unroll
+                    for (int oc = 0; oc < DX_OC; ++oc) {
+                        const float val = ld_shared_f32(st + (oc * DX_RH + row) * DX_GW);
+                        const float hi = tf32_hi(val);
+                        v[m][oc] = hi;
+                        v[m][16 + oc] = val - hi;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&g_empty[gs]);
+                PROF_MARK(1)
+                if (cc >= 2 && !mbar_wait_warp(&a_empty[as], ((cc >> 1) - 1) & 1, d.status, 62)) { ok = false; break; }
+                tc_fence_after_sync();
+                PROF_MARK(2)
+                const uint32_t a_addr = tmem_base + (uint32_t(quarter * 32) << 16) + A_COL0 + uint32_t(as) * 128 + uint32_t(2 * half) * 32;
+                tmem_st_32x32(a_addr, v[0]);
+                tmem_st_32x32(a_addr + 32, v[1]);
+                tmem_st_wait();
+                tc_fence_before_sync();
+                mbar_arrive(&a_full[as]);
+                PROF_MARK(3)
+            }
+            if (!ok) break;
+        }
+        if (tid == 128) PROF_DUMP(0)
+    } else if (warp == 14 && lane == 0) {
+        // ---- TMA loads of the g chunks ----
+        for (int it = 0; it < my_tiles; ++it) {
+            const int tile = blockIdx.x + it * gridDim.x;
+            const int img = tile / tiles_per_img, tt = tile % tiles_per_img;
+            const int x0 = (tt % d.tiles_x) * DX_TW, y0 = (tt / d.tiles_x) * DX_TH;
+            bool ok = true;
+            for (int q = 0; q < NCH; ++q) {
+                const int cc = it * NCH + q, gs = cc % DX_GS;
+                if (cc >= DX_GS && !mbar_wait(&g_empty[gs], ((cc / DX_GS) - 1) & 1, d.status, 63)) { ok = false; break; }
+                mbar_arrive_expect_tx(&g_full[gs], DX_GSTAGE * 4);
+                tma_load_4d(g_stages + gs * DX_GSTAGE, &map_g, &g_full[gs], x0 - 4, y0 - 1, q * DX_OC, img);
+            }
+            if (!ok) break;
+        }
+    } else if (warp == 12 || warp == 13) {
+        // ---- MMA issue: this warp's two M-tiles, every chunk.  The whole warp runs the loop and
+        // the thread chosen by elect.sync issues: with warp-uniform control flow the operands
+        // stay in uniform registers and one warp issues a small-N MMA every ~22 cycles
+        // (measured; 44 behind a lane == 0 branch, 81 with a per-instruction lane test). ----
+        const int mw = warp - 12;
+        const bool issue = elect_one();
+        const uint32_t idesc = idesc_tf32(128, 32, false, false);
+        const uint64_t db_hi0 = smem_desc(smem_u32(b_hi), 16, 1024, kLayoutSw128);
+        const uint64_t db_lo0 = smem_desc(smem_u32(b_lo), 16, 1024, kLayoutSw128);
+        PROF_DECL
+        for (int it = 0; it < my_tiles; ++it) {
+            const int db = it & 1;
+            bool ok = true;
+            for (int q = 0; q < NCH; ++q) {
+                const int cc = it * NCH + q, as = cc & 1;
+                if (!mbar_wait_warp(&a_full[as], (cc >> 1) & 1, d.status, 64)) { ok = false; break; }
+                PROF_MARK(0)
+                if (q == 0 && it >= 2 && !mbar_wait_warp(&d_empty[db], ((it >> 1) - 1) & 1, d.status, 65)) { ok = false; break; }
+                tc_fence_after_sync();
+                PROF_MARK(1)
+#pragma unroll
+                for (int m = 0; m < 2; ++m) {
+                    const int j = 2 * mw + m;
+                    const uint32_t acc = tmem_base + uint32_t(db) * 128 + uint32_t(j) * 32;
+                    const uint32_t a_hi = tmem_base + A_COL0 + uint32_t(as) * 128 + uint32_t(j) * 32, a_lo = a_hi + 16;
+#pragma unroll
+                    for (int ks = 0; ks < 2; ++ks) {
+                        const uint64_t off = uint64_t(((q >> 1) * 4096 + ((q & 1) * 2 + ks) * 32) >> 4);
+                        const bool first = q == 0 && ks == 0;
+                        if (issue) {
+                            if (d.three_pass) {
+                                mma_tf32_ts(acc, a_lo + 8 * ks, db_hi0 + off, idesc, !first);
+                                mma_tf32_ts(acc, a_hi + 8 * ks, db_lo0 + off, idesc, true);
+                                mma_tf32_ts(acc, a_hi + 8 * ks, db_hi0 + off, idesc, true);
+                            } else {
+                                mma_tf32_ts(acc, a_hi + 8 * ks, db_hi0 + off, idesc, !first);
+                            }
+                        }
+                    }
+                }
+                if (issue) {
+                    mma_commit(&a_empty[as]);
+                    if (q == NCH - 1) mma_commit(&d_full[db]);
+                }
+                __syncwarp();
+                PROF_MARK(2)
+            }
+            if (!ok) break;
+        }
+        if (mw == 0 && lane == 0) PROF_DUMP(1)
+    } else if (warp < 4) {
+        // ---- epilogue: Z out of TMEM into [tap][pixel] planes, col2im gather, TMA store ----
+        const int quarter = warp;
+        const size_t plane = size_t(d.h) * d.w;
+        PROF_DECL
+        for (int it = 0; it < my_tiles; ++it) {
+            const int db = it & 1;
+            if (!mbar_wait_warp(&d_full[db], (it >> 1) & 1, d.status, 66)) break;
+            tc_fence_after_sync();
+            PROF_MARK(0)
+            const int tile = blockIdx.x + it * gridDim.x;
+            const int img = tile / tiles_per_img, tt = tile % tiles_per_img;
+            const int x0 = (tt % d.tiles_x) * DX_TW, y0 = (tt / d.tiles_x) * DX_TH;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float v[32];
+                tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(db) * 128 + uint32_t(j) * 32, v);
+                float *zp = zs + (4 * j + quarter) * DX_RW + lane;
+#pragma unroll
+                for (int t = 0; t < TAPS; ++t) st_shared_f32(zp + t * DX_ZP, v[t]);
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&d_empty[db]);
+            if (tid == 0) tma_store_wait_read<0>();  // the previous tile's store has read `outs`
+            named_barrier(1, 128);
+            PROF_MARK(1)
+            if (lane < DX_TW) {
+                for (int iy = warp; iy < DX_TH; iy += 4) {
+                    const float *zr = zs + (iy + 2) * DX_RW + lane + 2;
+#pragma unroll
+                    for (int c = 0; c < CIN; ++c) {
+                        float acc = 0.f;
+#pragma unroll
+                        for (int ky = 0; ky < 3; ++ky)
+#pragma unroll
+                            for (int kx = 0; kx < 3; ++kx)
+                                acc += ld_shared_f32(zr + ((c * 3 + ky) * 3 + kx) * DX_ZP - ky * DX_RW - kx);
+                        if (d.accumulate) {
+                            const int gy = y0 + iy, gx = x0 + lane;
+                            if (gy < d.h && gx < d.w) acc = dx[(size_t(img) * CIN + c) * plane + size_t(gy) * d.w + gx] + acc;
+                        }
+                        st_shared_f32(outs + (c * DX_TH + iy) * DX_TW + lane, acc);
+                    }
+                }
+            }
+            fence_proxy_async_smem();
+            named_barrier(1, 128);
+            PROF_MARK(2)
+            if (tid == 0) {
+                tma_store_4d(&map_dx, outs, x0, y0, 0, img);
+                tma_store_commit();
+            }
+        }
+        if (tid == 0) PROF_DUMP(2)
+        if (tid == 0) tma_store_wait_all<0>();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 12) tmem_dealloc(tmem_base, 512);
+}
+
+template <int CIN>
+int32_t dx_launch(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx, StemDxDims d) {
+    CUtensorMap map_g, map_dx;
+    {
+        const uint64_t dims[4] = {(uint64_t)d.w, (uint64_t)d.h, (uint64_t)d.k, (uint64_t)d.n};
+        const uint64_t strides[4] = {1, (uint64_t)d.w, (uint64_t)d.w * d.h, (uint64_t)d.w * d.h * d.k};
+        const uint32_t box[4] = {DX_GW, DX_RH, DX_OC, 1};
+        if (!katsu_make_tensor_map(&map_g, g, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (stem dX g)");
+    }
+    {
+        const uint64_t dims[4] = {(uint64_t)d.w, (uint64_t)d.h, (uint64_t)CIN, (uint64_t)d.n};
+        const uint64_t strides[4] = {1, (uint64_t)d.w, (uint64_t)d.w * d.h, (uint64_t)d.w * d.h * CIN};
+        const uint32_t box[4] = {DX_TW, DX_TH, CIN, 1};
+        if (!katsu_make_tensor_map(&map_dx, dx, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (stem dX out)");
+    }
+    const size_t smem = size_t(d.kblocks) * 8192 + size_t(DX_GS) * DX_GSTAGE * 4 + size_t(CIN) * 9 * DX_ZP * 4 +
+                        size_t(CIN) * DX_TH * DX_TW * 4 + 1024;
+    auto kernel = stem_dx_tc_kernel<CIN>;
+    KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const size_t total_tiles = size_t(d.n) * d.tiles_x * d.tiles_y;
+    size_t grid = size_t(ctx->num_sms);
+    if (grid > total_tiles) grid = total_tiles;
+    KATSU_LAUNCH(ctx, kernel, (unsigned)grid, DX_THREADS, smem, w, dx, map_g, map_dx, d);
+    return KATSU_OK;
+}
+
+}  // namespace
+
+int32_t katsu_conv_stem_tc_dx(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx, size_t n, size_t c,
+                              size_t h, size_t wd, size_t k, int accumulate, int *handled) {
+    *handled = 0;
+    if (ctx->precision == KATSU_MODE_FP32) return KATSU_OK;
+    if (c < 1 || c > 3 || k < 1 || k > 128 || h > 32768 || wd > 32768 || wd % 4 != 0) return KATSU_OK;
+    if ((reinterpret_cast<uintptr_t>(g) & 15u) != 0 || (reinterpret_cast<uintptr_t>(dx) & 15u) != 0) return KATSU_OK;
+    StemDxDims d;
+    d.n = (int)n; d.k = (int)k; d.h = (int)h; d.w = (int)wd;
+    d.tiles_x = (int)katsu_div_up(wd, DX_TW);
+    d.tiles_y = (int)katsu_div_up(h, DX_TH);
+    if (n * size_t(d.tiles_x) * d.tiles_y > 0x3fffffffu / 8) return KATSU_OK;  // chunk counters stay in int
+    d.chunks = (int)katsu_div_up(k, DX_OC);
+    d.kblocks = (int)katsu_div_up(k, 32);
+    d.three_pass = ctx->precision == KATSU_MODE_3XTF32 ? 1 : 0;
+    d.accumulate = accumulate;
+    d.status = ctx->status;
+    *handled = 1;
+    switch (c) {
+        case 1: return dx_launch<1>(ctx, w, g, dx, d);
+        case 2: return dx_launch<2>(ctx, w, g, dx, d);
+        default: return dx_launch<3>(ctx, w, g, dx, d);
+    }
+}

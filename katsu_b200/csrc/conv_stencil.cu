@@ -439,7 +439,8 @@ int32_t katsu_conv_stencil_bwd(katsu_cuda_ctx *ctx, const float *x, const float 
     *handled = 1;
     StencilDims d = {(int)n, (int)k, (int)h, (int)wd, (int)katsu_div_up(wd, (size_t)TW), 0};
     int dx_done = 0;
-    if (dx != nullptr) KATSU_TRY(katsu_stencil_dx_tma(ctx, w, g, dx, n, c, h, wd, k, accumulate, &dx_done));
+    if (dx != nullptr) KATSU_TRY(katsu_conv_stem_tc_dx(ctx, w, g, dx, n, c, h, wd, k, accumulate, &dx_done));
+    if (dx != nullptr && !dx_done) KATSU_TRY(katsu_stencil_dx_tma(ctx, w, g, dx, n, c, h, wd, k, accumulate, &dx_done));
     if (dx != nullptr && !dx_done) {
         switch (c) {
             case 1: KATSU_TRY(dx_launch<1>(ctx, w, g, dx, d, accumulate)); break;
