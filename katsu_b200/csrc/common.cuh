@@ -137,6 +137,9 @@ int32_t katsu_conv_stem_tc_fwd(katsu_cuda_ctx *ctx, const float *x, const float 
 int32_t katsu_conv_stem_tc_dx(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx, size_t n, size_t c,
                               size_t h, size_t wd, size_t k, int accumulate, int *handled);
 
+int32_t katsu_conv_stem_tc_dw(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw, size_t n, size_t c,
+                              size_t h, size_t wd, size_t k, int accumulate, int *handled);
+
 // TMA-fed dX stencil (conv_stencil_tma.cu); *handled = 0 when TMA cannot describe g.
 int32_t katsu_stencil_dx_tma(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx, size_t n, size_t c,
                              size_t h, size_t wd, size_t k, int accumulate, int *handled);

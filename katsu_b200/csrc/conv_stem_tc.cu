@@ -101,12 +101,12 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
 
     if (tid == 0) {
         for (int s = 0; s < 3; ++s) {
-            mbar_init(&full[s], 128);
+            mbar_init(&full[s], 4);
             mbar_init(&empty[s], 1);
         }
         for (int s = 0; s < 4; ++s) {
             mbar_init(&acc_full[s], 1);
-            mbar_init(&acc_empty[s], 128);
+            mbar_init(&acc_empty[s], 4);
         }
         for (int s = 0; s < XS; ++s) {
             mbar_init(&x_full[s], 1);
@@ -176,7 +176,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
             if (d.three_pass) tmem_st_32x32(a_addr + 32, lo);
             tmem_st_wait();
             tc_fence_before_sync();
-            mbar_arrive(&full[s]);
+            mbar_arrive_warp(&full[s]);
             PROF_MARK(3)
         }
         if (r == 0 && group == 0) PROF_DUMP(0)
@@ -264,7 +264,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
                 }
                 if (c0 + 64 >= d.np) {
                     tc_fence_before_sync();
-                    mbar_arrive(&acc_empty[b]);  // the accumulator is free as soon as it has been read
+                    mbar_arrive_warp(&acc_empty[b]);  // the accumulator is free as soon as it has been read
                 }
                 PROF_MARK(1)
                 named_barrier(bar_id, 128);

@@ -92,10 +92,10 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
             mbar_init(&g_empty[s], 8);
         }
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&a_full[s], 256);
+            mbar_init(&a_full[s], 8);
             mbar_init(&a_empty[s], 2);
             mbar_init(&d_full[s], 2);
-            mbar_init(&d_empty[s], 128);
+            mbar_init(&d_empty[s], 4);
         }
         mbar_init_fence();
     }
@@ -157,7 +157,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
                 tmem_st_32x32(a_addr + 32, v[1]);
                 tmem_st_wait();
                 tc_fence_before_sync();
-                mbar_arrive(&a_full[as]);
+                mbar_arrive_warp(&a_full[as]);
                 PROF_MARK(3)
             }
             if (!ok) break;
@@ -251,7 +251,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
                 for (int t = 0; t < TAPS; ++t) st_shared_f32(zp + t * DX_ZP, v[t]);
             }
             tc_fence_before_sync();
-            mbar_arrive(&d_empty[db]);
+            mbar_arrive_warp(&d_empty[db]);
             if (tid == 0) tma_store_wait_read<0>();  // the previous tile's store has read `outs`
             named_barrier(1, 128);
             PROF_MARK(1)
@@ -318,6 +318,309 @@ int32_t dx_launch(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx
     return KATSU_OK;
 }
 
+
+// ---------------------------------------------------------------------------------------
+// dW:  dW[oc, tap] = sum_pixel g[oc, pixel] * Xcol[tap, pixel]   (a GEMM whose K is the pixel index)
+//   A = [g_hi ; g_lo], 128 rows (64 oc twice) x 32 pixels per K-block, in TENSOR MEMORY
+//       (lane = row, column = pixel), written by builder warps from the g row segment TMA
+//       dropped into shared memory ([64 oc][32 px], 128-byte-swizzled rows so that 32 lanes
+//       reading 32 different rows do not collide on banks).
+//   B = [Xcol_hi ; Xcol_lo], 64 rows (32 taps twice) x 32 pixels, K-major swizzled rows in
+//       shared memory, built from the x halo tile (the shifted windows cannot be loaded by
+//       TMA: a shift of one pixel is not a 16-byte step).
+//   D = 128 x 64: rows 0-63 hold hi*hi | hi*lo, rows 64-127 hold lo*hi | (lo*lo, unused).
+//       One MMA per 8 pixels does all of 3xTF32.  Two accumulators alternate K-blocks and are
+//       drained into registers every DW_DRAIN K-blocks, which bounds the length of any
+//       tensor-core accumulation chain (its f32 adds lose a little per step) to 2048 pixels.
+//   Each block ends with one partial dW in scratch; a second kernel folds the partials in a
+//   fixed order (bit-reproducible, no atomics).
+struct StemDwDims {
+    int n, k, h, w;
+    int tiles_x, tiles_y;   // 32-pixel columns, 4-row bands
+    int three_pass;
+    int *status;
+};
+
+constexpr int DW_GS = 6;                 // g K-block stages (8 KiB each)
+constexpr int DW_BS = 4;                 // B stages (8 KiB each)
+constexpr int DW_AS = 4;                 // A stages in TMEM (32 columns each)
+constexpr int DW_XS = 3;                 // x halo tiles in flight
+constexpr int DW_DRAIN = 128;            // K-blocks per drain period
+constexpr int DW_THREADS = 13 * 32;
+constexpr uint32_t DW_A_COL0 = 128;      // TMEM: [2 accumulators x 64][4 A stages x 32] = 256 columns
+constexpr int DW_MMA_WARP = 11;  // warp 12 issues the TMA loads
+
+// Warp roles: 0-3 and 4-7 two groups of A builders that alternate K-blocks (TMEM lane quarter
+// = warp & 3; a group's chain load -> split -> tcgen05.st -> wait is several hundred cycles
+// per K-block, two chains in flight per block hide it); group 0 also drains the accumulators.
+// 8-10 B builders, 11 MMA issue, 12 TMA loads.  Two blocks share an SM (256 TMEM columns each),
+// so the running sums of the drains live in shared memory, not registers.
+template <int CIN>
+__global__ void __launch_bounds__(DW_THREADS, 2)
+stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_x,
+                  float *__restrict__ partial, StemDwDims d) {
+    constexpr int TAPS = CIN * 9;
+    constexpr int XT = (CIN * 6 * 40 + 31) / 32 * 32;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char *g_stages = smem;                           // DW_GS x 8 KiB
+    unsigned char *b_stages = g_stages + DW_GS * 8192;        // DW_BS x 8 KiB
+    float *sums = reinterpret_cast<float *>(b_stages + DW_BS * 8192);  // [32 columns][128 rows]
+    float *x_tiles = sums + 32 * 128;                         // DW_XS x XT floats
+    __shared__ uint64_t g_full[DW_GS], g_empty[DW_GS], b_full[DW_BS], b_empty[DW_BS], a_full[DW_AS], a_empty[DW_AS],
+        x_full[DW_XS], x_empty[DW_XS], d_full, d_empty;
+    __shared__ uint32_t tmem_slot;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tiles_per_img = d.tiles_x * d.tiles_y;
+    const int total_tiles = d.n * tiles_per_img;
+    const int my_tiles = (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int my_kblocks = my_tiles * 4;
+
+    if (tid == 0) {
+        for (int s = 0; s < DW_GS; ++s) { mbar_init(&g_full[s], 1); mbar_init(&g_empty[s], 4); }
+        for (int s = 0; s < DW_BS; ++s) { mbar_init(&b_full[s], 3); mbar_init(&b_empty[s], 1); }
+        for (int s = 0; s < DW_AS; ++s) { mbar_init(&a_full[s], 4); mbar_init(&a_empty[s], 1); }
+        for (int s = 0; s < DW_XS; ++s) { mbar_init(&x_full[s], 1); mbar_init(&x_empty[s], 3); }
+        mbar_init(&d_full, 1);
+        mbar_init(&d_empty, 4);
+        mbar_init_fence();
+    }
+    if (warp == DW_MMA_WARP) {
+        tmem_alloc(&tmem_slot, 256);
+        tmem_relinquish();
+    }
+    // rows of B that no tap writes (27..31 and 59..63) stay zero for the whole kernel; sums start at zero
+    for (int i = tid; i < (DW_BS * 8192 + 32 * 128 * 4) / 16; i += DW_THREADS)
+        st_shared_v4(b_stages + i * 16, make_float4(0.f, 0.f, 0.f, 0.f));
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp < 8) {
+        // ---- A builders: thread = one row of A (oc = row % 64; rows >= 64 carry the lo parts) ----
+        const int group = warp >> 2, quarter = warp & 3, row = quarter * 32 + lane, oc = row & 63;
+        const bool is_lo = quarter >= 2;
+        const uint32_t lane_addr = tmem_base + (uint32_t(quarter * 32) << 16);
+        // drain of period p (group 0 only): fold both accumulators into the running sums in
+        // shared memory, then hand the accumulators back to the MMA warp
+        auto drain = [&](int p) -> bool {
+            if (!mbar_wait_warp(&d_full, p & 1, d.status, 73)) return false;
+            tc_fence_after_sync();
+            const int in_period = (my_kblocks - p * DW_DRAIN) < DW_DRAIN ? (my_kblocks - p * DW_DRAIN) : DW_DRAIN;
+            for (int a = 0; a < 2 && a < in_period; ++a) {
+                // rows < 64: hi*hi (columns 0-31) and hi*lo (32-63); rows >= 64: lo*hi (0-31)
+                for (int h = 0; h < (is_lo ? 1 : 2); ++h) {
+                    float t0[32];
+                    tmem_ld_32x32(lane_addr + uint32_t(a) * 64 + uint32_t(h) * 32, t0);
+#pragma unroll
+                    for (int t = 0; t < 32; ++t) st_shared_f32(sums + t * 128 + row, ld_shared_f32(sums + t * 128 + row) + t0[t]);
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive_warp(&d_empty);
+            return true;
+        };
+        PROF_DECL
+        bool ok = true;
+        for (int kb = group; kb < my_kblocks; kb += 2) {
+            if (group == 0 && kb > 0 && kb % DW_DRAIN == 0 && !drain(kb / DW_DRAIN - 1)) { ok = false; break; }
+            const int gs = kb % DW_GS, as = kb % DW_AS;
+            if (!mbar_wait_warp(&g_full[gs], (kb / DW_GS) & 1, d.status, 71)) { ok = false; break; }
+            PROF_MARK(0)
+            const unsigned char *grow = g_stages + gs * 8192 + oc * 128;
+            float v[32];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const float4 q = ld_shared_v4(grow + ((c ^ (oc & 7)) << 4));
+                v[4 * c] = q.x; v[4 * c + 1] = q.y; v[4 * c + 2] = q.z; v[4 * c + 3] = q.w;
+            }
+            // hi rows go in as they are: the tensor core reads only the TF32 part of an operand
+            // (it truncates), so the explicit split is needed for the lo rows alone
+            if (is_lo) {
+                if (d.three_pass) {
+#pragma unroll
+                    for (int t = 0; t < 32; ++t) v[t] -= tf32_hi(v[t]);
+                } else {
+#pragma unroll
+                    for (int t = 0; t < 32; ++t) v[t] = 0.f;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&g_empty[gs]);
+            PROF_MARK(1)
+            if (kb >= DW_AS && !mbar_wait_warp(&a_empty[as], ((kb / DW_AS) - 1) & 1, d.status, 72)) { ok = false; break; }
+            tc_fence_after_sync();
+            PROF_MARK(2)
+            tmem_st_32x32(lane_addr + DW_A_COL0 + uint32_t(as) * 32, v);
+            tmem_st_wait();
+            tc_fence_before_sync();
+            mbar_arrive_warp(&a_full[as]);
+            PROF_MARK(3)
+        }
+        if (tid == 0) PROF_DUMP(0)
+        if (group == 0) {
+            if (ok) drain((my_kblocks - 1) / DW_DRAIN);
+            // combine the hi rows with the lo rows of the same oc and write this block's partial
+            named_barrier(1, 128);
+            if (!is_lo && oc < d.k) {
+                float *dst = partial + (size_t(blockIdx.x) * d.k + oc) * TAPS;
+#pragma unroll
+                for (int t = 0; t < TAPS; ++t) dst[t] = ld_shared_f32(sums + t * 128 + oc) + ld_shared_f32(sums + t * 128 + 64 + oc);
+            }
+        }
+    } else if (warp < DW_MMA_WARP) {
+        // ---- B builders: task = (channel, ky, 4-pixel chunk); writes the three kx taps, hi and lo ----
+        const int task = (warp - 8) * 32 + lane;
+        const int cky = task >> 3, j = task & 7;
+        const bool active = cky < CIN * 3;
+        const int c = cky / 3, ky = cky - 3 * c;
+        int off_hi[3];  // byte offsets of this task's three chunks inside a B stage (lo rows: + 4096)
+#pragma unroll
+        for (int kx = 0; kx < 3; ++kx) {
+            const int t = cky * 3 + kx;
+            off_hi[kx] = t * 128 + ((j ^ (t & 7)) << 4);
+        }
+        const int src_off = (c * 6 + ky) * 40 + 4 * j + 3;
+        PROF_DECL
+        for (int it = 0; it < my_tiles; ++it) {
+            const int xs = it % DW_XS;
+            if (!mbar_wait_warp(&x_full[xs], (it / DW_XS) & 1, d.status, 74)) break;
+            PROF_MARK(0)
+            bool ok = true;
+            for (int r = 0; r < 4; ++r) {
+                const int kb = it * 4 + r, bs = kb % DW_BS;
+                float f[6];
+                if (active) {
+                    const float *src = x_tiles + xs * XT + src_off + r * 40;
+                    f[0] = ld_shared_f32(src);
+                    const float4 q = ld_shared_v4(src + 1);
+                    f[1] = q.x; f[2] = q.y; f[3] = q.z; f[4] = q.w;
+                    f[5] = ld_shared_f32(src + 5);
+                }
+                PROF_MARK(1)
+                if (kb >= DW_BS && !mbar_wait_warp(&b_empty[bs], ((kb / DW_BS) - 1) & 1, d.status, 75)) { ok = false; break; }
+                PROF_MARK(2)
+                if (active) {
+                    unsigned char *bt = b_stages + bs * 8192;
+                    float lo[6];
+#pragma unroll
+                    for (int e = 0; e < 6; ++e) lo[e] = d.three_pass ? f[e] - tf32_hi(f[e]) : 0.f;
+#pragma unroll
+                    for (int kx = 0; kx < 3; ++kx) {
+                        st_shared_v4(bt + off_hi[kx], make_float4(f[kx], f[kx + 1], f[kx + 2], f[kx + 3]));
+                        st_shared_v4(bt + off_hi[kx] + 4096, make_float4(lo[kx], lo[kx + 1], lo[kx + 2], lo[kx + 3]));
+                    }
+                }
+                fence_proxy_async_smem();
+                mbar_arrive_warp(&b_full[bs]);
+                PROF_MARK(3)
+            }
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&x_empty[xs]);
+        }
+        if (tid == 256) PROF_DUMP(1)
+    } else if (warp == DW_MMA_WARP) {
+        // ---- MMA issue (whole warp runs the loop, the elected thread issues) ----
+        const bool issue = elect_one();
+        const uint32_t idesc = idesc_tf32(128, 64, false, false);
+        const uint64_t bdesc0 = smem_desc(smem_u32(b_stages), 16, 1024, kLayoutSw128);
+        PROF_DECL
+        for (int kb = 0; kb < my_kblocks; ++kb) {
+            const int as = kb % DW_AS, bs = kb % DW_BS;
+            if (!mbar_wait_warp(&a_full[as], (kb / DW_AS) & 1, d.status, 76)) break;
+            if (!mbar_wait_warp(&b_full[bs], (kb / DW_BS) & 1, d.status, 77)) break;
+            PROF_MARK(0)
+            const int period = kb / DW_DRAIN, in_period = kb - period * DW_DRAIN;
+            if (in_period == 0 && period > 0 && !mbar_wait_warp(&d_empty, (period - 1) & 1, d.status, 78)) break;
+            tc_fence_after_sync();
+            PROF_MARK(1)
+            const uint32_t acc = tmem_base + uint32_t(kb & 1) * 64;
+            const uint32_t a_addr = tmem_base + DW_A_COL0 + uint32_t(as) * 32;
+            const uint64_t bdesc = bdesc0 + uint64_t((bs * 8192) >> 4);
+            if (issue) {
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+                    mma_tf32_ts(acc, a_addr + 8 * ks, bdesc + uint64_t(2 * ks), idesc, !(in_period < 2 && ks == 0));
+                mma_commit(&a_empty[as]);
+                mma_commit(&b_empty[bs]);
+                if (in_period == DW_DRAIN - 1 || kb + 1 == my_kblocks) mma_commit(&d_full);
+            }
+            __syncwarp();
+            PROF_MARK(2)
+        }
+        if (lane == 0) PROF_DUMP(2)
+    } else if (lane == 0) {
+        // ---- TMA loads: one x halo tile per 4-row tile, one g row segment per K-block ----
+        for (int it = 0; it < my_tiles; ++it) {
+            const int tile = blockIdx.x + it * gridDim.x;
+            const int img = tile / tiles_per_img, tt = tile % tiles_per_img;
+            const int ox0 = (tt % d.tiles_x) * 32, oy0 = (tt / d.tiles_x) * 4;
+            const int xs = it % DW_XS;
+            if (it >= DW_XS && !mbar_wait(&x_empty[xs], ((it / DW_XS) - 1) & 1, d.status, 79)) break;
+            mbar_arrive_expect_tx(&x_full[xs], CIN * 6 * 40 * 4);
+            tma_load_4d(x_tiles + xs * XT, &map_x, &x_full[xs], ox0 - 4, oy0 - 1, 0, img);
+            bool ok = true;
+            for (int r = 0; r < 4; ++r) {
+                const int kb = it * 4 + r, gs = kb % DW_GS;
+                if (kb >= DW_GS && !mbar_wait(&g_empty[gs], ((kb / DW_GS) - 1) & 1, d.status, 80)) { ok = false; break; }
+                mbar_arrive_expect_tx(&g_full[gs], 8192);
+                tma_load_4d(g_stages + gs * 8192, &map_g, &g_full[gs], ox0, oy0 + r, 0, img);
+            }
+            if (!ok) break;
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == DW_MMA_WARP) tmem_dealloc(tmem_base, 256);
+}
+
+__global__ void __launch_bounds__(256)
+stem_dw_fold_kernel(const float *__restrict__ partial, float *dw, int elems, int parts, int accumulate) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= elems) return;
+    float s = 0.f;
+    for (int p = 0; p < parts; ++p) s += partial[size_t(p) * elems + i];
+    dw[i] = accumulate ? dw[i] + s : s;
+}
+
+template <int CIN>
+int32_t dw_launch(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw, StemDwDims d, int accumulate) {
+    CUtensorMap map_g, map_x;
+    {
+        const uint64_t dims[4] = {(uint64_t)d.w, (uint64_t)d.h, (uint64_t)d.k, (uint64_t)d.n};
+        const uint64_t strides[4] = {1, (uint64_t)d.w, (uint64_t)d.w * d.h, (uint64_t)d.w * d.h * d.k};
+        const uint32_t box[4] = {32, 1, 64, 1};
+        if (!katsu_make_tensor_map(&map_g, g, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (stem dW g)");
+    }
+    {
+        const uint64_t dims[4] = {(uint64_t)d.w, (uint64_t)d.h, (uint64_t)CIN, (uint64_t)d.n};
+        const uint64_t strides[4] = {1, (uint64_t)d.w, (uint64_t)d.w * d.h, (uint64_t)d.w * d.h * CIN};
+        const uint32_t box[4] = {40, 6, CIN, 1};
+        if (!katsu_make_tensor_map(&map_x, x, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (stem dW x)");
+    }
+    constexpr int XT = (CIN * 6 * 40 + 31) / 32 * 32;
+    // at least 100 KiB so that a third block (which could not get TMEM columns) is never co-resident
+    size_t smem = size_t(DW_GS + DW_BS) * 8192 + 32 * 128 * 4 + size_t(DW_XS) * XT * 4 + 1024;
+    if (smem < 100 * 1024) smem = 100 * 1024;
+    auto kernel = stem_dw_tc_kernel<CIN>;
+    KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const size_t total_tiles = size_t(d.n) * d.tiles_x * d.tiles_y;
+    size_t grid = size_t(ctx->num_sms) * 2;
+    if (grid > total_tiles) grid = total_tiles;
+    const int elems = d.k * CIN * 9;
+    float *partial = nullptr;
+    KATSU_TRY(katsu_scratch(ctx, grid * elems, &partial));
+    KATSU_LAUNCH(ctx, kernel, (unsigned)grid, DW_THREADS, smem, map_g, map_x, partial, d);
+    KATSU_LAUNCH(ctx, stem_dw_fold_kernel, (unsigned)katsu_div_up((size_t)elems, (size_t)256), 256, 0, partial, dw, elems,
+                 (int)grid, accumulate);
+    return KATSU_OK;
+}
+
 }  // namespace
 
 int32_t katsu_conv_stem_tc_dx(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx, size_t n, size_t c,
@@ -341,5 +644,26 @@ int32_t katsu_conv_stem_tc_dx(katsu_cuda_ctx *ctx, const float *w, const float *
         case 1: return dx_launch<1>(ctx, w, g, dx, d);
         case 2: return dx_launch<2>(ctx, w, g, dx, d);
         default: return dx_launch<3>(ctx, w, g, dx, d);
+    }
+}
+
+int32_t katsu_conv_stem_tc_dw(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw, size_t n, size_t c,
+                              size_t h, size_t wd, size_t k, int accumulate, int *handled) {
+    *handled = 0;
+    if (ctx->precision == KATSU_MODE_FP32) return KATSU_OK;
+    if (c < 1 || c > 3 || k < 1 || k > 64 || n == 0 || h > 32768 || wd > 32768 || wd % 4 != 0) return KATSU_OK;
+    if ((reinterpret_cast<uintptr_t>(g) & 15u) != 0 || (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return KATSU_OK;
+    StemDwDims d;
+    d.n = (int)n; d.k = (int)k; d.h = (int)h; d.w = (int)wd;
+    d.tiles_x = (int)katsu_div_up(wd, 32);
+    d.tiles_y = (int)katsu_div_up(h, 4);
+    if (n * size_t(d.tiles_x) * d.tiles_y > 0x3fffffffu / 4) return KATSU_OK;  // K-block counters stay in int
+    d.three_pass = ctx->precision == KATSU_MODE_3XTF32 ? 1 : 0;
+    d.status = ctx->status;
+    *handled = 1;
+    switch (c) {
+        case 1: return dw_launch<1>(ctx, x, g, dw, d, accumulate);
+        case 2: return dw_launch<2>(ctx, x, g, dw, d, accumulate);
+        default: return dw_launch<3>(ctx, x, g, dw, d, accumulate);
     }
 }

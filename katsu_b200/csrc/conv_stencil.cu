@@ -450,7 +450,8 @@ int32_t katsu_conv_stencil_bwd(katsu_cuda_ctx *ctx, const float *x, const float 
         }
     }
     int dw_done = 0;
-    if (dw != nullptr) KATSU_TRY(katsu_stencil_dw_tma(ctx, x, g, dw, n, c, h, wd, k, accumulate, &dw_done));
+    if (dw != nullptr) KATSU_TRY(katsu_conv_stem_tc_dw(ctx, x, g, dw, n, c, h, wd, k, accumulate, &dw_done));
+    if (dw != nullptr && !dw_done) KATSU_TRY(katsu_stencil_dw_tma(ctx, x, g, dw, n, c, h, wd, k, accumulate, &dw_done));
     if (dw != nullptr && !dw_done) {
         switch (c) {
             case 1: KATSU_TRY(dw_launch<1>(ctx, x, g, dw, d, accumulate)); break;

@@ -72,6 +72,18 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// One poll (the hardware may park the thread for a short, implementation-defined time).
+// Measured: an explicit suspend-time hint of 100 us made the pipelined stem kernels 3-5 %
+// slower, so none is given.
+// One arrival for the whole warp, after every lane has finished what the barrier guards.
+// 32 lanes arriving on one barrier are 32 serialised shared-memory operations; the pipelined
+// stem kernels hand off every few hundred cycles, where that was a large share of the
+// shared-memory pipe's time.  Barriers used this way are initialised with a count of warps.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t *bar) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
