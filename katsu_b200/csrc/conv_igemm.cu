@@ -155,32 +155,38 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 tma_load_4d(st + (2 + part) * TILE_BYTES, mb, &full[s], k0, n0, p.b_tap[t], 0);
             }
         }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
+        // MMA issue: whole warp in the loop, the elect.sync thread issues (uniform control flow
+        // keeps operands in uniform registers and makes waits on full stages cheap)
+        const bool issue = elect_one();
         const uint32_t idesc = idesc_tf32(BM, BN, false, false);
         for (int i = 0; i < kblocks; ++i) {
             const int s = i % STAGES;
-            if (!mbar_wait(&full[s], (i / STAGES) & 1, p.status, 22)) break;
+            if (!mbar_wait_warp_ready(&full[s], (i / STAGES) & 1, p.status, 22)) break;
             tc_fence_after_sync();
             const uint32_t st = smem_u32(smem + s * stage_bytes);
             const uint32_t acc = tmem_base + uint32_t(i % NACC) * BN;
             const bool first = i < NACC;
+            if (issue) {
 #pragma unroll
-            for (int j = 0; j < BK / 8; ++j) {
-                const uint64_t a_hi = smem_desc(st + j * 32, 16, 1024, kLayoutSw128);
-                const uint64_t b_hi = smem_desc(st + 2 * TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
-                if (p.three_pass) {
-                    const uint64_t a_lo = smem_desc(st + TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
-                    const uint64_t b_lo = smem_desc(st + 3 * TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
-                    mma_tf32(acc, a_lo, b_hi, idesc, !(first && j == 0));
-                    mma_tf32(acc, a_hi, b_lo, idesc, true);
-                    mma_tf32(acc, a_hi, b_hi, idesc, true);
-                } else {
-                    mma_tf32(acc, a_hi, b_hi, idesc, !(first && j == 0));
+                for (int j = 0; j < BK / 8; ++j) {
+                    const uint64_t a_hi = smem_desc(st + j * 32, 16, 1024, kLayoutSw128);
+                    const uint64_t b_hi = smem_desc(st + 2 * TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
+                    if (p.three_pass) {
+                        const uint64_t a_lo = smem_desc(st + TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
+                        const uint64_t b_lo = smem_desc(st + 3 * TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
+                        mma_tf32(acc, a_lo, b_hi, idesc, !(first && j == 0));
+                        mma_tf32(acc, a_hi, b_lo, idesc, true);
+                        mma_tf32(acc, a_hi, b_hi, idesc, true);
+                    } else {
+                        mma_tf32(acc, a_hi, b_hi, idesc, !(first && j == 0));
+                    }
                 }
+                mma_commit(&empty[s]);
             }
-            mma_commit(&empty[s]);
+            __syncwarp();
         }
-        mma_commit(&done);
+        if (issue) mma_commit(&done);
     }
     __syncwarp();
 
@@ -307,39 +313,45 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
                                 ox0 * p.stride + p.off_x[tap], oy0 * p.stride + p.off_y[tap], img);
             }
         }
-    } else if (warp == 5 && lane == 0) {
+    } else if (warp == 5) {
+        // MMA issue: whole warp in the loop, the elect.sync thread issues
+        const bool issue = elect_one();
         const uint32_t idesc = idesc_tf32(BM, BN, true, true);
         bool ok = true;
         for (int b = 0; b < batches && ok; ++b) {
             // the previous batch's accumulators must have been read out by all 128 threads
-            if (b > 0 && !mbar_wait(&drained, (b - 1) & 1, p.status, 33)) break;
+            if (b > 0 && !mbar_wait_warp(&drained, (b - 1) & 1, p.status, 33)) break;
             tc_fence_after_sync();
             const int i_end = (b + 1) * DRAIN < kblocks ? (b + 1) * DRAIN : kblocks;
             for (int i = b * DRAIN; i < i_end; ++i) {
                 const int s = i % STAGES;
-                if (!mbar_wait(&full[s], (i / STAGES) & 1, p.status, 32)) { ok = false; break; }
+                if (!mbar_wait_warp_ready(&full[s], (i / STAGES) & 1, p.status, 32)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t st = smem_u32(smem + s * stage_bytes);
                 const int li = i - b * DRAIN;
                 const uint32_t acc = tmem_base + uint32_t(li % NACC) * BN;
                 const bool first = li < NACC;
+                if (issue) {
 #pragma unroll
-                for (int j = 0; j < BK / 8; ++j) {
-                    const uint64_t a_hi = smem_desc(st + j * 1024, 4096, 512, kLayoutSw128Base32);
-                    const uint64_t b_hi = smem_desc(st + 2 * TILE_BYTES + j * 1024, 4096, 512, kLayoutSw128Base32);
-                    if (p.three_pass) {
-                        const uint64_t a_lo = smem_desc(st + TILE_BYTES + j * 1024, 4096, 512, kLayoutSw128Base32);
-                        const uint64_t b_lo = smem_desc(st + 3 * TILE_BYTES + j * 1024, 4096, 512, kLayoutSw128Base32);
-                        mma_tf32(acc, a_lo, b_hi, idesc, !(first && j == 0));
-                        mma_tf32(acc, a_hi, b_lo, idesc, true);
-                        mma_tf32(acc, a_hi, b_hi, idesc, true);
-                    } else {
-                        mma_tf32(acc, a_hi, b_hi, idesc, !(first && j == 0));
+                    for (int j = 0; j < BK / 8; ++j) {
+                        const uint64_t a_hi = smem_desc(st + j * 1024, 4096, 512, kLayoutSw128Base32);
+                        const uint64_t b_hi = smem_desc(st + 2 * TILE_BYTES + j * 1024, 4096, 512, kLayoutSw128Base32);
+                        if (p.three_pass) {
+                            const uint64_t a_lo = smem_desc(st + TILE_BYTES + j * 1024, 4096, 512, kLayoutSw128Base32);
+                            const uint64_t b_lo = smem_desc(st + 3 * TILE_BYTES + j * 1024, 4096, 512, kLayoutSw128Base32);
+                            mma_tf32(acc, a_lo, b_hi, idesc, !(first && j == 0));
+                            mma_tf32(acc, a_hi, b_lo, idesc, true);
+                            mma_tf32(acc, a_hi, b_hi, idesc, true);
+                        } else {
+                            mma_tf32(acc, a_hi, b_hi, idesc, !(first && j == 0));
+                        }
                     }
+                    mma_commit(&empty[s]);
                 }
-                mma_commit(&empty[s]);
+                __syncwarp();
             }
-            if (ok) mma_commit(&batch_done);
+            if (ok && issue) mma_commit(&batch_done);
+            __syncwarp();
         }
     }
     __syncwarp();

@@ -91,6 +91,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
     __shared__ __align__(128) float x_tiles[XS][XT];                   // [c][6 rows][40 columns]
     __shared__ uint64_t full[3], empty[3], acc_full[4], acc_empty[4], x_full[XS], x_empty[XS];
     __shared__ uint32_t tmem_slot;
+    __shared__ int epilogue_dead[2];  // per epilogue group: a warp's wait ran out; read after the named barrier
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles_per_img = d.tiles_x * d.tiles_y;
     const int total_tiles = d.n * tiles_per_img;
@@ -112,6 +113,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
             mbar_init(&x_full[s], 1);
             mbar_init(&x_empty[s], 4);
         }
+        epilogue_dead[0] = epilogue_dead[1] = 0;
         mbar_init_fence();
     }
     if (warp == MMA_WARP) {
@@ -245,14 +247,18 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
         PROF_DECL
         for (int it = group; it < my_tiles; it += GROUPS) {
             const int b = it % NB;
-            if (!mbar_wait_warp(&acc_full[b], (it / NB) & 1, d.status, 44)) break;
+            // A warp whose wait ran out still meets its group at the named barrier (the others may
+            // have got through just before); the group then leaves together.
+            if (!mbar_wait_warp(&acc_full[b], (it / NB) & 1, d.status, 44) && lane == 0) epilogue_dead[group] = 1;
             tc_fence_after_sync();
+            bool quit = false;
             PROF_MARK(0)
             const int tile = blockIdx.x + it * gridDim.x;
             const int img = tile / tiles_per_img, tt = tile % tiles_per_img;
             const int oy0 = (tt / d.tiles_x) * 4, ox0 = (tt % d.tiles_x) * 32;
             for (int c0 = 0; c0 < d.np; c0 += 64) {
                 named_barrier(bar_id, 128);  // the previous pass has been copied out of the staging buffer
+                if (*reinterpret_cast<volatile int *>(&epilogue_dead[group])) { quit = true; break; }
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     if (c0 + 32 * h < d.np) {
@@ -280,6 +286,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
                 }
                 PROF_MARK(3)
             }
+            if (quit) break;
         }
         if (r == 0 && group == 0) PROF_DUMP(2)
     }

@@ -80,6 +80,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
     float *outs = zs + TAPS * DX_ZP;
     __shared__ uint64_t g_full[DX_GS], g_empty[DX_GS], a_full[2], a_empty[2], d_full[2], d_empty[2];
     __shared__ uint32_t tmem_slot;
+    __shared__ int epilogue_dead;  // set by an epilogue warp whose wait ran out; read after the named barrier
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles_per_img = d.tiles_x * d.tiles_y;
     const int total_tiles = d.n * tiles_per_img;
@@ -97,6 +98,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
             mbar_init(&d_full[s], 2);
             mbar_init(&d_empty[s], 4);
         }
+        epilogue_dead = 0;
         mbar_init_fence();
     }
     if (warp == 12) {
@@ -131,7 +133,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
             bool ok = true;
             for (int q = 0; q < NCH; ++q) {
                 const int cc = it * NCH + q, gs = cc % DX_GS, as = cc & 1;
-                if (!mbar_wait_warp(&g_full[gs], (cc / DX_GS) & 1, d.status, 61)) { ok = false; break; }
+                if (!mbar_wait_warp_ready(&g_full[gs], (cc / DX_GS) & 1, d.status, 61)) { ok = false; break; }
                 PROF_MARK(0)
                 const float *st = g_stages + gs * DX_GSTAGE + 3 + lane;
                 float v[2][32];
@@ -149,7 +151,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&g_empty[gs]);
                 PROF_MARK(1)
-                if (cc >= 2 && !mbar_wait_warp(&a_empty[as], ((cc >> 1) - 1) & 1, d.status, 62)) { ok = false; break; }
+                if (cc >= 2 && !mbar_wait_warp_ready(&a_empty[as], ((cc >> 1) - 1) & 1, d.status, 62)) { ok = false; break; }
                 tc_fence_after_sync();
                 PROF_MARK(2)
                 const uint32_t a_addr = tmem_base + (uint32_t(quarter * 32) << 16) + A_COL0 + uint32_t(as) * 128 + uint32_t(2 * half) * 32;
@@ -194,9 +196,9 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
             bool ok = true;
             for (int q = 0; q < NCH; ++q) {
                 const int cc = it * NCH + q, as = cc & 1;
-                if (!mbar_wait_warp(&a_full[as], (cc >> 1) & 1, d.status, 64)) { ok = false; break; }
+                if (!mbar_wait_warp_ready(&a_full[as], (cc >> 1) & 1, d.status, 64)) { ok = false; break; }
                 PROF_MARK(0)
-                if (q == 0 && it >= 2 && !mbar_wait_warp(&d_empty[db], ((it >> 1) - 1) & 1, d.status, 65)) { ok = false; break; }
+                if (q == 0 && it >= 2 && !mbar_wait_warp_ready(&d_empty[db], ((it >> 1) - 1) & 1, d.status, 65)) { ok = false; break; }
                 tc_fence_after_sync();
                 PROF_MARK(1)
 #pragma unroll
@@ -236,24 +238,31 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
         PROF_DECL
         for (int it = 0; it < my_tiles; ++it) {
             const int db = it & 1;
-            if (!mbar_wait_warp(&d_full[db], (it >> 1) & 1, d.status, 66)) break;
+            // A warp whose wait ran out must still meet the others at the named barrier (they
+            // may have got through just before); all four then leave together.
+            const bool alive = mbar_wait_warp_ready(&d_full[db], (it >> 1) & 1, d.status, 66);
             tc_fence_after_sync();
             PROF_MARK(0)
             const int tile = blockIdx.x + it * gridDim.x;
             const int img = tile / tiles_per_img, tt = tile % tiles_per_img;
             const int x0 = (tt % d.tiles_x) * DX_TW, y0 = (tt / d.tiles_x) * DX_TH;
+            if (alive) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float v[32];
-                tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(db) * 128 + uint32_t(j) * 32, v);
-                float *zp = zs + (4 * j + quarter) * DX_RW + lane;
+                for (int j = 0; j < 4; ++j) {
+                    float v[32];
+                    tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(db) * 128 + uint32_t(j) * 32, v);
+                    float *zp = zs + (4 * j + quarter) * DX_RW + lane;
 #pragma unroll
-                for (int t = 0; t < TAPS; ++t) st_shared_f32(zp + t * DX_ZP, v[t]);
+                    for (int t = 0; t < TAPS; ++t) st_shared_f32(zp + t * DX_ZP, v[t]);
+                }
+                tc_fence_before_sync();
+                mbar_arrive_warp(&d_empty[db]);
+            } else if (lane == 0) {
+                epilogue_dead = 1;
             }
-            tc_fence_before_sync();
-            mbar_arrive_warp(&d_empty[db]);
             if (tid == 0) tma_store_wait_read<0>();  // the previous tile's store has read `outs`
             named_barrier(1, 128);
+            if (*reinterpret_cast<volatile int *>(&epilogue_dead)) break;
             PROF_MARK(1)
             if (lane < DX_TW) {
                 for (int iy = warp; iy < DX_TH; iy += 4) {
@@ -342,7 +351,7 @@ struct StemDwDims {
 };
 
 constexpr int DW_GS = 6;                 // g K-block stages (8 KiB each)
-constexpr int DW_BS = 4;                 // B stages (8 KiB each)
+constexpr int DW_BS = 4;                 // B stages (8 KiB each); must equal DW_AS (shared barriers)
 constexpr int DW_AS = 4;                 // A stages in TMEM (32 columns each)
 constexpr int DW_XS = 3;                 // x halo tiles in flight
 constexpr int DW_DRAIN = 128;            // K-blocks per drain period
@@ -367,8 +376,8 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
     unsigned char *b_stages = g_stages + DW_GS * 8192;        // DW_BS x 8 KiB
     float *sums = reinterpret_cast<float *>(b_stages + DW_BS * 8192);  // [32 columns][128 rows]
     float *x_tiles = sums + 32 * 128;                         // DW_XS x XT floats
-    __shared__ uint64_t g_full[DW_GS], g_empty[DW_GS], b_full[DW_BS], b_empty[DW_BS], a_full[DW_AS], a_empty[DW_AS],
-        x_full[DW_XS], x_empty[DW_XS], d_full, d_empty;
+    __shared__ uint64_t g_full[DW_GS], g_empty[DW_GS], ab_full[DW_AS], ab_empty[DW_AS], x_full[DW_XS], x_empty[DW_XS], d_full,
+        d_empty;
     __shared__ uint32_t tmem_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles_per_img = d.tiles_x * d.tiles_y;
@@ -378,8 +387,9 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
 
     if (tid == 0) {
         for (int s = 0; s < DW_GS; ++s) { mbar_init(&g_full[s], 1); mbar_init(&g_empty[s], 4); }
-        for (int s = 0; s < DW_BS; ++s) { mbar_init(&b_full[s], 3); mbar_init(&b_empty[s], 1); }
-        for (int s = 0; s < DW_AS; ++s) { mbar_init(&a_full[s], 4); mbar_init(&a_empty[s], 1); }
+        // one barrier pair per stage for A and B together (4 A-builder warps + 3 B-builder warps
+        // fill it, one commit frees it): every wait in the MMA warp's loop costs ~90 cycles
+        for (int s = 0; s < DW_AS; ++s) { mbar_init(&ab_full[s], 7); mbar_init(&ab_empty[s], 1); }
         for (int s = 0; s < DW_XS; ++s) { mbar_init(&x_full[s], 1); mbar_init(&x_empty[s], 3); }
         mbar_init(&d_full, 1);
         mbar_init(&d_empty, 4);
@@ -406,7 +416,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
         // drain of period p (group 0 only): fold both accumulators into the running sums in
         // shared memory, then hand the accumulators back to the MMA warp
         auto drain = [&](int p) -> bool {
-            if (!mbar_wait_warp(&d_full, p & 1, d.status, 73)) return false;
+            if (!mbar_wait_warp_ready(&d_full, p & 1, d.status, 73)) return false;
             tc_fence_after_sync();
             const int in_period = (my_kblocks - p * DW_DRAIN) < DW_DRAIN ? (my_kblocks - p * DW_DRAIN) : DW_DRAIN;
             for (int a = 0; a < 2 && a < in_period; ++a) {
@@ -427,7 +437,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
         for (int kb = group; kb < my_kblocks; kb += 2) {
             if (group == 0 && kb > 0 && kb % DW_DRAIN == 0 && !drain(kb / DW_DRAIN - 1)) { ok = false; break; }
             const int gs = kb % DW_GS, as = kb % DW_AS;
-            if (!mbar_wait_warp(&g_full[gs], (kb / DW_GS) & 1, d.status, 71)) { ok = false; break; }
+            if (!mbar_wait_warp_ready(&g_full[gs], (kb / DW_GS) & 1, d.status, 71)) { ok = false; break; }
             PROF_MARK(0)
             const unsigned char *grow = g_stages + gs * 8192 + oc * 128;
             float v[32];
@@ -450,13 +460,13 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(&g_empty[gs]);
             PROF_MARK(1)
-            if (kb >= DW_AS && !mbar_wait_warp(&a_empty[as], ((kb / DW_AS) - 1) & 1, d.status, 72)) { ok = false; break; }
+            if (kb >= DW_AS && !mbar_wait_warp_ready(&ab_empty[as], ((kb / DW_AS) - 1) & 1, d.status, 72)) { ok = false; break; }
             tc_fence_after_sync();
             PROF_MARK(2)
             tmem_st_32x32(lane_addr + DW_A_COL0 + uint32_t(as) * 32, v);
             tmem_st_wait();
             tc_fence_before_sync();
-            mbar_arrive_warp(&a_full[as]);
+            mbar_arrive_warp(&ab_full[as]);
             PROF_MARK(3)
         }
         if (tid == 0) PROF_DUMP(0)
@@ -486,7 +496,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
         PROF_DECL
         for (int it = 0; it < my_tiles; ++it) {
             const int xs = it % DW_XS;
-            if (!mbar_wait_warp(&x_full[xs], (it / DW_XS) & 1, d.status, 74)) break;
+            if (!mbar_wait_warp_ready(&x_full[xs], (it / DW_XS) & 1, d.status, 74)) break;
             PROF_MARK(0)
             bool ok = true;
             for (int r = 0; r < 4; ++r) {
@@ -500,7 +510,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
                     f[5] = ld_shared_f32(src + 5);
                 }
                 PROF_MARK(1)
-                if (kb >= DW_BS && !mbar_wait_warp(&b_empty[bs], ((kb / DW_BS) - 1) & 1, d.status, 75)) { ok = false; break; }
+                if (kb >= DW_BS && !mbar_wait_warp_ready(&ab_empty[bs], ((kb / DW_BS) - 1) & 1, d.status, 75)) { ok = false; break; }
                 PROF_MARK(2)
                 if (active) {
                     unsigned char *bt = b_stages + bs * 8192;
@@ -514,7 +524,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
                     }
                 }
                 fence_proxy_async_smem();
-                mbar_arrive_warp(&b_full[bs]);
+                mbar_arrive_warp(&ab_full[bs]);
                 PROF_MARK(3)
             }
             if (!ok) break;
@@ -530,11 +540,10 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
         PROF_DECL
         for (int kb = 0; kb < my_kblocks; ++kb) {
             const int as = kb % DW_AS, bs = kb % DW_BS;
-            if (!mbar_wait_warp(&a_full[as], (kb / DW_AS) & 1, d.status, 76)) break;
-            if (!mbar_wait_warp(&b_full[bs], (kb / DW_BS) & 1, d.status, 77)) break;
+            if (!mbar_wait_warp_ready(&ab_full[as], (kb / DW_AS) & 1, d.status, 76)) break;
             PROF_MARK(0)
             const int period = kb / DW_DRAIN, in_period = kb - period * DW_DRAIN;
-            if (in_period == 0 && period > 0 && !mbar_wait_warp(&d_empty, (period - 1) & 1, d.status, 78)) break;
+            if (in_period == 0 && period > 0 && !mbar_wait_warp_ready(&d_empty, (period - 1) & 1, d.status, 78)) break;
             tc_fence_after_sync();
             PROF_MARK(1)
             const uint32_t acc = tmem_base + uint32_t(kb & 1) * 64;
@@ -544,8 +553,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
                     mma_tf32_ts(acc, a_addr + 8 * ks, bdesc + uint64_t(2 * ks), idesc, !(in_period < 2 && ks == 0));
-                mma_commit(&a_empty[as]);
-                mma_commit(&b_empty[bs]);
+                mma_commit(&ab_empty[as]);
                 if (in_period == DW_DRAIN - 1 || kb + 1 == my_kblocks) mma_commit(&d_full);
             }
             __syncwarp();
