@@ -91,7 +91,6 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
     __shared__ __align__(128) float x_tiles[XS][XT];                   // [c][6 rows][40 columns]
     __shared__ uint64_t full[3], empty[3], acc_full[4], acc_empty[4], x_full[XS], x_empty[XS];
     __shared__ uint32_t tmem_slot;
-    __shared__ int epilogue_dead[2];  // per epilogue group: a warp's wait ran out; read after the named barrier
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles_per_img = d.tiles_x * d.tiles_y;
     const int total_tiles = d.n * tiles_per_img;
@@ -113,7 +112,6 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
             mbar_init(&x_full[s], 1);
             mbar_init(&x_empty[s], 4);
         }
-        epilogue_dead[0] = epilogue_dead[1] = 0;
         mbar_init_fence();
     }
     if (warp == MMA_WARP) {
@@ -245,37 +243,37 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
         const int bar_id = 1 + group;
         float *stage = out_stages + group * (64 * 128);
         PROF_DECL
+        bool alive = true;
         for (int it = group; it < my_tiles; it += GROUPS) {
             const int b = it % NB;
-            // A warp whose wait ran out still meets its group at the named barrier (the others may
-            // have got through just before); the group then leaves together.
-            if (!mbar_wait_warp(&acc_full[b], (it / NB) & 1, d.status, 44) && lane == 0) epilogue_dead[group] = 1;
+            // A warp whose wait ran out keeps meeting its group at the named barriers (the others
+            // may have got through just before) and skips the work; once one wait of the launch
+            // has failed all later waits return at once, so the rest of the loop is quick.
+            if (alive) alive = mbar_wait_warp(&acc_full[b], (it / NB) & 1, d.status, 44);
             tc_fence_after_sync();
-            bool quit = false;
             PROF_MARK(0)
             const int tile = blockIdx.x + it * gridDim.x;
             const int img = tile / tiles_per_img, tt = tile % tiles_per_img;
             const int oy0 = (tt / d.tiles_x) * 4, ox0 = (tt % d.tiles_x) * 32;
             for (int c0 = 0; c0 < d.np; c0 += 64) {
                 named_barrier(bar_id, 128);  // the previous pass has been copied out of the staging buffer
-                if (*reinterpret_cast<volatile int *>(&epilogue_dead[group])) { quit = true; break; }
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    if (c0 + 32 * h < d.np) {
+                    if (alive && c0 + 32 * h < d.np) {
                         float v[32];
                         tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + b * d.np + c0 + 32 * h, v);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) st_shared_f32(stage + (32 * h + i) * 128 + r, v[i]);
                     }
                 }
-                if (c0 + 64 >= d.np) {
+                if (alive && c0 + 64 >= d.np) {
                     tc_fence_before_sync();
                     mbar_arrive_warp(&acc_empty[b]);  // the accumulator is free as soon as it has been read
                 }
                 PROF_MARK(1)
                 named_barrier(bar_id, 128);
                 PROF_MARK(2)
-                const int chans = (d.k - c0) < 64 ? (d.k - c0) : 64;
+                const int chans = !alive ? 0 : (d.k - c0) < 64 ? (d.k - c0) : 64;
                 for (int f = r; f < chans * 32; f += 128) {
                     const int oc = f >> 5, row = (f >> 3) & 3, col = (f & 7) * 4;
                     const int oy = oy0 + row, ox = ox0 + col;
@@ -286,7 +284,6 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
                 }
                 PROF_MARK(3)
             }
-            if (quit) break;
         }
         if (r == 0 && group == 0) PROF_DUMP(2)
     }

@@ -80,7 +80,6 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
     float *outs = zs + TAPS * DX_ZP;
     __shared__ uint64_t g_full[DX_GS], g_empty[DX_GS], a_full[2], a_empty[2], d_full[2], d_empty[2];
     __shared__ uint32_t tmem_slot;
-    __shared__ int epilogue_dead;  // set by an epilogue warp whose wait ran out; read after the named barrier
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles_per_img = d.tiles_x * d.tiles_y;
     const int total_tiles = d.n * tiles_per_img;
@@ -98,7 +97,6 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
             mbar_init(&d_full[s], 2);
             mbar_init(&d_empty[s], 4);
         }
-        epilogue_dead = 0;
         mbar_init_fence();
     }
     if (warp == 12) {
@@ -235,12 +233,14 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
         // ---- epilogue: Z out of TMEM into [tap][pixel] planes, col2im gather, TMA store ----
         const int quarter = warp;
         const size_t plane = size_t(d.h) * d.w;
+        bool alive = true;
         PROF_DECL
         for (int it = 0; it < my_tiles; ++it) {
             const int db = it & 1;
-            // A warp whose wait ran out must still meet the others at the named barrier (they
-            // may have got through just before); all four then leave together.
-            const bool alive = mbar_wait_warp_ready(&d_full[db], (it >> 1) & 1, d.status, 66);
+            // A warp whose wait ran out keeps meeting the others at the named barriers (they may
+            // have got through just before) and skips the work; once one wait of the launch has
+            // failed all later waits return at once, so the rest of the loop is quick.
+            if (alive) alive = mbar_wait_warp_ready(&d_full[db], (it >> 1) & 1, d.status, 66);
             tc_fence_after_sync();
             PROF_MARK(0)
             const int tile = blockIdx.x + it * gridDim.x;
@@ -257,14 +257,11 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
                 }
                 tc_fence_before_sync();
                 mbar_arrive_warp(&d_empty[db]);
-            } else if (lane == 0) {
-                epilogue_dead = 1;
             }
             if (tid == 0) tma_store_wait_read<0>();  // the previous tile's store has read `outs`
             named_barrier(1, 128);
-            if (*reinterpret_cast<volatile int *>(&epilogue_dead)) break;
             PROF_MARK(1)
-            if (lane < DX_TW) {
+            if (alive && lane < DX_TW) {
                 for (int iy = warp; iy < DX_TH; iy += 4) {
                     const float *zr = zs + (iy + 2) * DX_RW + lane + 2;
 #pragma unroll
@@ -286,7 +283,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
             fence_proxy_async_smem();
             named_barrier(1, 128);
             PROF_MARK(2)
-            if (tid == 0) {
+            if (tid == 0 && alive) {
                 tma_store_4d(&map_dx, outs, x0, y0, 0, img);
                 tma_store_commit();
             }

@@ -110,7 +110,12 @@ __device__ __forceinline__ bool mbar_wait_budget(uint64_t *bar, uint32_t parity,
     const long long start = clock64();
     for (uint32_t i = 0; i < kWaitPolls; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63u) == 63u && clock64() - start > cycles) break;
+        if ((i & 63u) == 63u) {
+            // once any wait of the launch has given up, the others follow at once instead of
+            // each running out its own budget
+            if (status != nullptr && *reinterpret_cast<volatile int *>(status) != 0) return false;
+            if (clock64() - start > cycles) break;
+        }
     }
     if (status != nullptr) atomicCAS(status, 0, code);
     return false;
