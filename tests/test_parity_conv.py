@@ -26,6 +26,11 @@ SHAPES = [
     (1, 3, 8, 8, 8, 3, 3, 1, 1), (2, 3, 33, 37, 5, 3, 3, 1, 1), (1, 1, 40, 64, 70, 3, 3, 1, 1),
     (2, 4, 9, 36, 9, 3, 3, 1, 1), (3, 2, 17, 5, 64, 3, 3, 1, 1), (2, 3, 64, 64, 32, 3, 3, 1, 1),
     (1, 3, 31, 224, 64, 3, 3, 1, 1), (5, 3, 7, 3, 130, 3, 3, 1, 1),
+    # low-channel tensor-core backward (C <= 3, width a multiple of 4): heights and widths that leave
+    # partial 14x28 / 4x32 tiles, channel counts that leave partial 16- and 32-channel chunks, K beyond
+    # the dW kernel's 64 (dX on tensor cores, dW on the stencil), every C
+    (2, 3, 30, 36, 17, 3, 3, 1, 1), (1, 2, 45, 100, 64, 3, 3, 1, 1), (3, 1, 15, 60, 100, 3, 3, 1, 1),
+    (1, 3, 57, 28, 33, 3, 3, 1, 1), (2, 3, 14, 28, 16, 3, 3, 1, 1),
 ]
 
 
@@ -61,7 +66,8 @@ def test_conv_matches_oracle(ctx, oracle, shape, accumulate):
         assert err <= REL_L2_TOL, (name, err, shape)
 
 
-@pytest.mark.parametrize("shape", [(2, 32, 14, 14, 48, 3, 3, 1, 1), (1, 64, 16, 16, 32, 3, 3, 2, 1)],
+@pytest.mark.parametrize("shape", [(2, 32, 14, 14, 48, 3, 3, 1, 1), (1, 64, 16, 16, 32, 3, 3, 2, 1),
+                                   (2, 3, 40, 64, 48, 3, 3, 1, 1)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_conv_tf32_mode(ctx, oracle, shape):
     """Opt-in single-pass TF32 mode on the tensor-core path: within 2e-3, and measurably
