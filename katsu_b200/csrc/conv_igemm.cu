@@ -97,32 +97,54 @@ struct IgemmParams {
     short off_y[MAX_TAPS], off_x[MAX_TAPS], b_tap[MAX_TAPS];
 };
 
-__global__ void __launch_bounds__(128, 1)
+// Persistent: one block per SM walks (pixel tile, channel tile) pairs.  BNT = 128 / 64 / 32 output
+// channels per tile, chosen by the launch from the channel count so that narrow layers do not
+// pay for 128-wide MMAs and operand tiles.  Warps 0-3 are the epilogue (TMEM lane quarter =
+// warp), warp 4 issues the TMA loads, warp 5 the MMAs.  Two accumulator sets alternate between
+// tiles so a tile's epilogue runs under the next tile's k-loop; a set is NACC_T rotating
+// accumulators (2 of 128 columns, or 4 of 64 / 32).
+template <int BNT>
+struct IgemmCfg {
+    static constexpr int NACC_T = BNT == 128 ? 2 : 4;
+    static constexpr int SET_COLS = NACC_T * BNT;
+    static constexpr int TMEM_COLS = 2 * SET_COLS;                 // 512, 512, 256
+    static constexpr int B_BYTES = BNT * BK * 4;
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES + 2 * B_BYTES;  // A hi | A lo | B hi | B lo
+    static constexpr int STAGES_T = BNT == 128 ? 3 : 4;
+    static constexpr size_t SMEM = size_t(STAGES_T) * STAGE_BYTES + 1024;
+};
+
+template <int BNT>
+__global__ void __launch_bounds__(192, 1)
 conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_lo,
                   const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_b_lo,
-                  const __grid_constant__ IgemmParams p) {
+                  const __grid_constant__ IgemmParams p, int m_tiles, int n_tiles) {
+    using Cfg = IgemmCfg<BNT>;
+    constexpr int NACC_T = Cfg::NACC_T, STAGES_T = Cfg::STAGES_T;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ uint64_t full[STAGES], empty[STAGES], done;
+    __shared__ uint64_t full[STAGES_T], empty[STAGES_T], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_slot;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BN;
     const int blocks_per_img = p.blocks_x * p.blocks_y;
     const int kchunks = (p.kc + BK - 1) / BK;
     const int kblocks = p.ntaps * kchunks;
-    const int tiles_per_stage = p.three_pass ? 4 : 2;
-    const uint32_t stage_bytes = 4 * TILE_BYTES;
+    const int total_tiles = m_tiles * n_tiles;
+    const int my_tiles = (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < STAGES_T; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        mbar_init(&done, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
         mbar_init_fence();
     }
-    if (warp == 0) {
-        tmem_alloc(&tmem_slot, NACC * BN);
+    if (warp == 5) {
+        tmem_alloc(&tmem_slot, Cfg::TMEM_COLS);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -130,106 +152,127 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_slot;
 
-    if (warp == 0 && lane == 0) {
-        // block coordinates of the tile's two 64-pixel halves
-        int bn[2], by[2], bx[2];
-        for (int h = 0; h < 2; ++h) {
-            const long long gb = 2ll * blockIdx.y + h;
-            bn[h] = int(gb / blocks_per_img);  // == n_img for a block past the end: TMA zero-fills it
-            const int r = int(gb % blocks_per_img);
-            by[h] = r / p.blocks_x;
-            bx[h] = r % p.blocks_x;
-        }
-        for (int i = 0; i < kblocks; ++i) {
-            const int s = i % STAGES;
-            if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, p.status, 21)) break;
-            mbar_arrive_expect_tx(&full[s], tiles_per_stage * TILE_BYTES);
-            unsigned char *st = smem + s * stage_bytes;
-            const int t = i / kchunks, k0 = (i % kchunks) * BK;
-            for (int part = 0; part < (p.three_pass ? 2 : 1); ++part) {
-                const CUtensorMap *ma = part ? &map_a_lo : &map_a;
-                const CUtensorMap *mb = part ? &map_b_lo : &map_b;
-                for (int h = 0; h < 2; ++h)
-                    tma_load_4d(st + part * TILE_BYTES + h * (TILE_BYTES / 2), ma, &full[s], k0,
-                                bx[h] * p.bw * p.in_step + p.off_x[t], by[h] * p.bh * p.in_step + p.off_y[t], bn[h]);
-                tma_load_4d(st + (2 + part) * TILE_BYTES, mb, &full[s], k0, n0, p.b_tap[t], 0);
+    if (warp == 4 && lane == 0) {
+        // ---- TMA producer ----
+        bool ok = true;
+        for (int it = 0; it < my_tiles && ok; ++it) {
+            const int tile = blockIdx.x + it * gridDim.x;
+            const int mt = tile / n_tiles, n0 = (tile % n_tiles) * BNT;
+            // block coordinates of the tile's two 64-pixel halves
+            int bn[2], by[2], bx[2];
+            for (int h = 0; h < 2; ++h) {
+                const long long gb = 2ll * mt + h;
+                bn[h] = int(gb / blocks_per_img);  // == n_img for a block past the end: TMA zero-fills it
+                const int r = int(gb % blocks_per_img);
+                by[h] = r / p.blocks_x;
+                bx[h] = r % p.blocks_x;
+            }
+            for (int i = 0; i < kblocks; ++i) {
+                const int g = it * kblocks + i, s = g % STAGES_T;
+                if (g >= STAGES_T && !mbar_wait(&empty[s], ((g / STAGES_T) - 1) & 1, p.status, 21)) { ok = false; break; }
+                mbar_arrive_expect_tx(&full[s], (p.three_pass ? 2 : 1) * (TILE_BYTES + Cfg::B_BYTES));
+                unsigned char *st = smem + s * Cfg::STAGE_BYTES;
+                const int t = i / kchunks, k0 = (i % kchunks) * BK;
+                for (int part = 0; part < (p.three_pass ? 2 : 1); ++part) {
+                    const CUtensorMap *ma = part ? &map_a_lo : &map_a;
+                    const CUtensorMap *mb = part ? &map_b_lo : &map_b;
+                    for (int h = 0; h < 2; ++h)
+                        tma_load_4d(st + part * TILE_BYTES + h * (TILE_BYTES / 2), ma, &full[s], k0,
+                                    bx[h] * p.bw * p.in_step + p.off_x[t], by[h] * p.bh * p.in_step + p.off_y[t], bn[h]);
+                    tma_load_4d(st + 2 * TILE_BYTES + part * Cfg::B_BYTES, mb, &full[s], k0, n0, p.b_tap[t], 0);
+                }
             }
         }
-    } else if (warp == 1) {
-        // MMA issue: whole warp in the loop, the elect.sync thread issues (uniform control flow
-        // keeps operands in uniform registers and makes waits on full stages cheap)
+    } else if (warp == 5) {
+        // ---- MMA issue: whole warp in the loop, the elect.sync thread issues (uniform control
+        // flow keeps operands in uniform registers and makes waits on full stages cheap) ----
         const bool issue = elect_one();
-        const uint32_t idesc = idesc_tf32(BM, BN, false, false);
-        for (int i = 0; i < kblocks; ++i) {
-            const int s = i % STAGES;
-            if (!mbar_wait_warp_ready(&full[s], (i / STAGES) & 1, p.status, 22)) break;
+        const uint32_t idesc = idesc_tf32(BM, BNT, false, false);
+        bool ok = true;
+        for (int it = 0; it < my_tiles && ok; ++it) {
+            const int b = it & 1;
+            if (it >= 2 && !mbar_wait_warp(&acc_empty[b], ((it >> 1) - 1) & 1, p.status, 24)) break;
             tc_fence_after_sync();
-            const uint32_t st = smem_u32(smem + s * stage_bytes);
-            const uint32_t acc = tmem_base + uint32_t(i % NACC) * BN;
-            const bool first = i < NACC;
-            if (issue) {
+            for (int i = 0; i < kblocks; ++i) {
+                const int g = it * kblocks + i, s = g % STAGES_T;
+                if (!mbar_wait_warp_ready(&full[s], (g / STAGES_T) & 1, p.status, 22)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t st = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                const uint32_t acc = tmem_base + uint32_t(b) * Cfg::SET_COLS + uint32_t(i % NACC_T) * BNT;
+                const bool first = i < NACC_T;
+                if (issue) {
 #pragma unroll
-                for (int j = 0; j < BK / 8; ++j) {
-                    const uint64_t a_hi = smem_desc(st + j * 32, 16, 1024, kLayoutSw128);
-                    const uint64_t b_hi = smem_desc(st + 2 * TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
-                    if (p.three_pass) {
-                        const uint64_t a_lo = smem_desc(st + TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
-                        const uint64_t b_lo = smem_desc(st + 3 * TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
-                        mma_tf32(acc, a_lo, b_hi, idesc, !(first && j == 0));
-                        mma_tf32(acc, a_hi, b_lo, idesc, true);
-                        mma_tf32(acc, a_hi, b_hi, idesc, true);
-                    } else {
-                        mma_tf32(acc, a_hi, b_hi, idesc, !(first && j == 0));
+                    for (int j = 0; j < BK / 8; ++j) {
+                        const uint64_t a_hi = smem_desc(st + j * 32, 16, 1024, kLayoutSw128);
+                        const uint64_t b_hi = smem_desc(st + 2 * TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
+                        if (p.three_pass) {
+                            const uint64_t a_lo = smem_desc(st + TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
+                            const uint64_t b_lo = smem_desc(st + 2 * TILE_BYTES + Cfg::B_BYTES + j * 32, 16, 1024, kLayoutSw128);
+                            mma_tf32(acc, a_lo, b_hi, idesc, !(first && j == 0));
+                            mma_tf32(acc, a_hi, b_lo, idesc, true);
+                            mma_tf32(acc, a_hi, b_hi, idesc, true);
+                        } else {
+                            mma_tf32(acc, a_hi, b_hi, idesc, !(first && j == 0));
+                        }
                     }
+                    mma_commit(&empty[s]);
+                    if (i == kblocks - 1) mma_commit(&acc_full[b]);
                 }
-                mma_commit(&empty[s]);
+                __syncwarp();
             }
-            __syncwarp();
         }
-        if (issue) mma_commit(&done);
-    }
-    __syncwarp();
-
-    const bool finished = mbar_wait(&done, 0, p.status, 23);
-    tc_fence_after_sync();
-    if (finished && kblocks > 0) {
-        // this thread's pixel
+    } else if (warp < 4) {
+        // ---- epilogue: thread = pixel; accumulators summed in registers, 32 channels at a time ----
         const int r = warp * 32 + lane;
-        const long long gb = 2ll * blockIdx.y + (r >> 6);
-        const int img = int(gb / blocks_per_img);
-        const int rb = int(gb % blocks_per_img);
-        const int jy = (rb / p.blocks_x) * p.bh + (r & 63) / p.bw;
-        const int jx = (rb % p.blocks_x) * p.bw + (r & 63) % p.bw;
-        const bool pixel_ok = img < p.n_img && jy < p.grid_h && jx < p.grid_w;
-        const int oy = p.out_sy * jy + p.out_oy, ox = p.out_sx * jx + p.out_ox;
         const size_t plane = size_t(p.out_h) * p.out_w;
-        float *dst_px = p.out + size_t(img) * p.out_c * plane + size_t(oy) * p.out_w + ox;
-        const int used_acc = kblocks < NACC ? kblocks : NACC;
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-            if (n0 + c0 >= p.out_c) break;
-            float v[32];
-            tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + c0, v);
-            for (int a = 1; a < used_acc; ++a) {
-                float t[32];
-                tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + a * BN + c0, t);
+        const int used_acc = kblocks < NACC_T ? kblocks : NACC_T;
+        for (int it = 0; it < my_tiles; ++it) {
+            const int b = it & 1;
+            if (!mbar_wait_warp(&acc_full[b], (it >> 1) & 1, p.status, 23)) break;
+            tc_fence_after_sync();
+            const int tile = blockIdx.x + it * gridDim.x;
+            const int mt = tile / n_tiles, n0 = (tile % n_tiles) * BNT;
+            const long long gb = 2ll * mt + (r >> 6);
+            const int img = int(gb / blocks_per_img);
+            const int rb = int(gb % blocks_per_img);
+            const int jy = (rb / p.blocks_x) * p.bh + (r & 63) / p.bw;
+            const int jx = (rb % p.blocks_x) * p.bw + (r & 63) % p.bw;
+            const bool pixel_ok = img < p.n_img && jy < p.grid_h && jx < p.grid_w;
+            const int oy = p.out_sy * jy + p.out_oy, ox = p.out_sx * jx + p.out_ox;
+            float *dst_px = p.out + size_t(img) * p.out_c * plane + size_t(oy) * p.out_w + ox;
+            const uint32_t set = tmem_base + (uint32_t(warp * 32) << 16) + uint32_t(b) * Cfg::SET_COLS;
+            for (int c0 = 0; c0 < BNT; c0 += 32) {
+                const bool last_group = c0 + 32 >= BNT || n0 + c0 + 32 >= p.out_c;
+                float v[32];
+                tmem_ld_32x32(set + c0, v);
+                for (int a = 1; a < used_acc; ++a) {
+                    float t[32];
+                    tmem_ld_32x32(set + a * BNT + c0, t);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] += t[i];
-            }
-            if (pixel_ok) {
+                    for (int i = 0; i < 32; ++i) v[i] += t[i];
+                }
+                if (last_group) {
+                    // everything this tile needs from the accumulators is in registers now
+                    tc_fence_before_sync();
+                    mbar_arrive_warp(&acc_empty[b]);
+                }
+                if (pixel_ok) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int ch = n0 + c0 + i;
-                    if (ch < p.out_c) {
-                        float *dst = dst_px + size_t(ch) * plane;
-                        *dst = p.accumulate ? *dst + v[i] : v[i];
+                    for (int i = 0; i < 32; ++i) {
+                        const int ch = n0 + c0 + i;
+                        if (ch < p.out_c) {
+                            float *dst = dst_px + size_t(ch) * plane;
+                            *dst = p.accumulate ? *dst + v[i] : v[i];
+                        }
                     }
                 }
+                if (last_group) break;
             }
         }
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem_base, NACC * BN);
+    if (warp == 5) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
 // ---- dW kernel ------------------------------------------------------------------------
@@ -253,6 +296,7 @@ constexpr int DRAIN = NACC * 16;
 // 192 threads: warps 0-3 fold the accumulators (one TMEM lane quarter each), warp 4 feeds TMA,
 // warp 5 issues the MMAs.  The roles never share a thread, so the drain hand-shake cannot
 // wait on itself.
+template <int BNT>
 __global__ void __launch_bounds__(192, 1)
 conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_g_lo,
                      const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_x_lo,
@@ -262,8 +306,8 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
     __shared__ uint64_t full[STAGES], empty[STAGES], drained, batch_done;
     __shared__ uint32_t tmem_slot;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ctiles = (p.c + BN - 1) / BN;
-    const int c0 = (blockIdx.x % ctiles) * BN, k0 = (blockIdx.x / ctiles) * BM;
+    const int ctiles = (p.c + BNT - 1) / BNT;
+    const int c0 = (blockIdx.x % ctiles) * BNT, k0 = (blockIdx.x / ctiles) * BM;
     const int tap = blockIdx.y;
     const int groups_per_img = p.groups_x * p.groups_y;
     const long long total_groups = (long long)p.n_img * groups_per_img;
@@ -285,7 +329,7 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
         mbar_init_fence();
     }
     if (warp == 4) {
-        tmem_alloc(&tmem_slot, NACC * BN);
+        tmem_alloc(&tmem_slot, NACC * BNT);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -297,7 +341,7 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
         for (int i = 0; i < kblocks; ++i) {
             const int s = i % STAGES;
             if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, p.status, 31)) break;
-            mbar_arrive_expect_tx(&full[s], tiles_per_stage * TILE_BYTES);
+            mbar_arrive_expect_tx(&full[s], (p.three_pass ? 2 : 1) * (TILE_BYTES + BNT * BK * 4));
             unsigned char *st = smem + s * stage_bytes;
             const long long gidx = g_begin + i;
             const int img = int(gidx / groups_per_img);
@@ -308,7 +352,7 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
                 const CUtensorMap *mx = part ? &map_x_lo : &map_x;
                 for (int j = 0; j < BM / 32; ++j)
                     tma_load_4d(st + part * TILE_BYTES + j * 4096, mg, &full[s], k0 + 32 * j, ox0, oy0, img);
-                for (int j = 0; j < BN / 32; ++j)
+                for (int j = 0; j < BNT / 32; ++j)
                     tma_load_4d(st + (2 + part) * TILE_BYTES + j * 4096, mx, &full[s], c0 + 32 * j,
                                 ox0 * p.stride + p.off_x[tap], oy0 * p.stride + p.off_y[tap], img);
             }
@@ -316,7 +360,7 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
     } else if (warp == 5) {
         // MMA issue: whole warp in the loop, the elect.sync thread issues
         const bool issue = elect_one();
-        const uint32_t idesc = idesc_tf32(BM, BN, true, true);
+        const uint32_t idesc = idesc_tf32(BM, BNT, true, true);
         bool ok = true;
         for (int b = 0; b < batches && ok; ++b) {
             // the previous batch's accumulators must have been read out by all 128 threads
@@ -329,7 +373,7 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
                 tc_fence_after_sync();
                 const uint32_t st = smem_u32(smem + s * stage_bytes);
                 const int li = i - b * DRAIN;
-                const uint32_t acc = tmem_base + uint32_t(li % NACC) * BN;
+                const uint32_t acc = tmem_base + uint32_t(li % NACC) * BNT;
                 const bool first = li < NACC;
                 if (issue) {
 #pragma unroll
@@ -357,10 +401,10 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
     __syncwarp();
 
     if (warp < 4) {
-    // running sums of this thread's output row (oc = k0 + 32*warp + lane), 128 columns
-    float run[BN];
+    // running sums of this thread's output row (oc = k0 + 32*warp + lane), BNT columns
+    float run[BNT];
 #pragma unroll
-    for (int i = 0; i < BN; ++i) run[i] = 0.f;
+    for (int i = 0; i < BNT; ++i) run[i] = 0.f;
     bool alive = true;
     for (int b = 0; b < batches && alive; ++b) {
         alive = mbar_wait(&batch_done, b & 1, p.status, 34);
@@ -369,10 +413,10 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
             const int in_batch = (kblocks - b * DRAIN) < DRAIN ? (kblocks - b * DRAIN) : DRAIN;
             const int used_acc = in_batch < NACC ? in_batch : NACC;
 #pragma unroll
-            for (int q = 0; q < BN / 32; ++q) {
+            for (int q = 0; q < BNT / 32; ++q) {
                 for (int a = 0; a < used_acc; ++a) {
                     float t[32];
-                    tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + a * BN + q * 32, t);
+                    tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + a * BNT + q * 32, t);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) run[q * 32 + i] += t[i];
                 }
@@ -386,14 +430,14 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
         if (oc < p.k) {
             float *dst = p.partial + ((size_t(blockIdx.z) * p.taps + tap) * p.k + oc) * p.c;
 #pragma unroll
-            for (int i = 0; i < BN; ++i)
+            for (int i = 0; i < BNT; ++i)
                 if (c0 + i < p.c) dst[c0 + i] = alive ? run[i] : 0.f;
         }
     }
     }  // epilogue warps
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 4) tmem_dealloc(tmem_base, NACC * BN);
+    if (warp == 4) tmem_dealloc(tmem_base, NACC * BNT);
 }
 
 // dw[k][c][tap] (+)= sum over splits of partial[split][tap][k][c]
@@ -437,13 +481,13 @@ bool nhwc_map(CUtensorMap *map, const float *base, size_t n, size_t h, size_t w,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// [taps][rows][inner] weight staging array, box {32, 128, 1, 1} (4-D with a unit last dimension).
-bool taps_map(CUtensorMap *map, const float *base, size_t taps, size_t rows, size_t inner) {
+// [taps][rows][inner] weight staging array, box {32, box_rows, 1, 1} (4-D with a unit last dimension).
+bool taps_map(CUtensorMap *map, const float *base, size_t taps, size_t rows, size_t inner, int box_rows) {
     katsu_tensor_map_encode_fn encode = katsu_tensor_map_encoder();
     if (encode == nullptr) return false;
     cuuint64_t dims[4] = {inner, rows, taps, 1};
     cuuint64_t strides[3] = {inner * sizeof(float), rows * inner * sizeof(float), taps * rows * inner * sizeof(float)};
-    cuuint32_t box[4] = {32, BN, 1, 1};
+    cuuint32_t box[4] = {32, cuuint32_t(box_rows), 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -461,7 +505,7 @@ void pick_block(size_t width, int *bw, int *bh) {
     *bh = 64 / *bw;
 }
 
-constexpr size_t kSmemBytes = size_t(STAGES) * 4 * TILE_BYTES + 1024;
+constexpr size_t kSmemBytes = size_t(STAGES) * 4 * TILE_BYTES + 1024;  // dW kernel
 
 struct Shape {
     size_t n, c, h, w, k, r, s, stride, pad, oh, ow;
@@ -475,6 +519,32 @@ bool igemm_shape(const katsu_cuda_ctx *ctx, const Shape &g) {
     // too little work for 128x128 tiles: leave it to the direct kernels
     if (g.n * g.oh * g.ow < 64) return false;
     return katsu_tensor_map_encoder() != nullptr;
+}
+
+// Forward / dX launch: picks the channel-tile width, builds the B maps for it and starts one
+// persistent block per SM (or per tile, if there are fewer).
+template <int BNT>
+int32_t launch_igemm_bn(katsu_cuda_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &ma_lo, const float *b_hi,
+                        const float *b_lo, size_t taps, size_t rows, size_t inner, const IgemmParams &p,
+                        size_t total_blocks) {
+    CUtensorMap mb, mb_lo;
+    if (!taps_map(&mb, b_hi, taps, rows, inner, BNT) || !taps_map(&mb_lo, b_lo, taps, rows, inner, BNT))
+        return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv weights)");
+    auto kernel = conv_igemm_kernel<BNT>;
+    KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)IgemmCfg<BNT>::SMEM));
+    const size_t m_tiles = katsu_div_up(total_blocks, 2), n_tiles = katsu_div_up(rows, (size_t)BNT);
+    if (m_tiles * n_tiles > 0x7fffffffu / 64) return katsu_set_error(KATSU_ERR_UNSUPPORTED, "convolution too large for the tile counter");
+    size_t grid = m_tiles * n_tiles;
+    if (grid > (size_t)ctx->num_sms) grid = (size_t)ctx->num_sms;
+    KATSU_LAUNCH(ctx, kernel, (unsigned)grid, 192, IgemmCfg<BNT>::SMEM, ma, ma_lo, mb, mb_lo, p, (int)m_tiles, (int)n_tiles);
+    return KATSU_OK;
+}
+
+int32_t launch_igemm(katsu_cuda_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &ma_lo, const float *b_hi,
+                     const float *b_lo, size_t taps, size_t rows, size_t inner, const IgemmParams &p, size_t total_blocks) {
+    if (rows <= 32) return launch_igemm_bn<32>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
+    if (rows <= 64) return launch_igemm_bn<64>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
+    return launch_igemm_bn<128>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
 }
 
 }  // namespace
@@ -516,16 +586,12 @@ int32_t katsu_conv_igemm_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w
         p.off_x[t] = (short)((int)(t % s) - (int)pad);
         p.b_tap[t] = (short)t;
     }
-    CUtensorMap ma, ma_lo, mb, mb_lo;
+    CUtensorMap ma, ma_lo;
     bool ok = nhwc_map(&ma, xt, n, h, wd, c, p.bw, p.bh, (int)stride, CU_TENSOR_MAP_SWIZZLE_128B) &&
-              nhwc_map(&ma_lo, three ? xt_lo : xt, n, h, wd, c, p.bw, p.bh, (int)stride, CU_TENSOR_MAP_SWIZZLE_128B) &&
-              taps_map(&mb, wf, taps, k, c) && taps_map(&mb_lo, three ? wf_lo : wf, taps, k, c);
+              nhwc_map(&ma_lo, three ? xt_lo : xt, n, h, wd, c, p.bw, p.bh, (int)stride, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!ok) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv forward)");
-    KATSU_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
     const size_t total_blocks = n * p.blocks_x * p.blocks_y;
-    dim3 grid((unsigned)katsu_div_up(k, (size_t)BN), (unsigned)katsu_div_up(total_blocks, 2));
-    KATSU_LAUNCH(ctx, conv_igemm_kernel, grid, 128, kSmemBytes, ma, ma_lo, mb, mb_lo, p);
-    return KATSU_OK;
+    return launch_igemm(ctx, ma, ma_lo, wf, three ? wf_lo : wf, taps, k, c, p, total_blocks);
 }
 
 int32_t katsu_conv_igemm_dx(katsu_cuda_ctx *ctx, const float *w, const float *gr, float *dx,
@@ -545,7 +611,6 @@ int32_t katsu_conv_igemm_dx(katsu_cuda_ctx *ctx, const float *w, const float *gr
     KATSU_TRY(stage_nhwc(ctx, gr, gt, gt_lo, n, k, oh * ow));
     KATSU_LAUNCH(ctx, weights_to_taps_kernel, (unsigned)katsu_div_up(we, 256), 256, 0, w, (float *)nullptr,
                  (float *)nullptr, wb, wb_lo, (int)k, (int)c, (int)taps);
-    KATSU_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
 
     // One launch per parity class (py, px) of input pixels: iy = stride*jy + py receives
     // only taps with (py + pad - ky) divisible by stride, from g row jy + (py + pad - ky)/stride.
@@ -600,13 +665,11 @@ int32_t katsu_conv_igemm_dx(katsu_cuda_ctx *ctx, const float *w, const float *gr
             p.ntaps = nt;
             if (nt == 0) continue;
             const size_t total_blocks = n * p.blocks_x * p.blocks_y;
-            CUtensorMap ma, ma_lo, mb, mb_lo;
+            CUtensorMap ma, ma_lo;
             bool ok = nhwc_map(&ma, gt, n, oh, ow, k, p.bw, p.bh, 1, CU_TENSOR_MAP_SWIZZLE_128B) &&
-                      nhwc_map(&ma_lo, three ? gt_lo : gt, n, oh, ow, k, p.bw, p.bh, 1, CU_TENSOR_MAP_SWIZZLE_128B) &&
-                      taps_map(&mb, wb, taps, c, k) && taps_map(&mb_lo, three ? wb_lo : wb, taps, c, k);
+                      nhwc_map(&ma_lo, three ? gt_lo : gt, n, oh, ow, k, p.bw, p.bh, 1, CU_TENSOR_MAP_SWIZZLE_128B);
             if (!ok) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv dX)");
-            dim3 grid((unsigned)katsu_div_up(c, (size_t)BN), (unsigned)katsu_div_up(total_blocks, 2));
-            KATSU_LAUNCH(ctx, conv_igemm_kernel, grid, 128, kSmemBytes, ma, ma_lo, mb, mb_lo, p);
+            KATSU_TRY(launch_igemm(ctx, ma, ma_lo, wb, three ? wb_lo : wb, taps, c, k, p, total_blocks));
         }
     return KATSU_OK;
 }
@@ -632,7 +695,9 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr
         p.off_x[t] = (short)((int)(t % s) - (int)pad);
     }
     const size_t total_groups = n * p.groups_x * p.groups_y;
-    const size_t out_tiles = katsu_div_up(k, (size_t)BM) * katsu_div_up(c, (size_t)BN) * taps;
+    // channel-tile width of the c side: narrow layers get narrow MMAs and operand tiles
+    const size_t bnt = c <= 32 ? 32 : c <= 64 ? 64 : 128;
+    const size_t out_tiles = katsu_div_up(k, (size_t)BM) * katsu_div_up(c, bnt) * taps;
     // Split the pixel range so that the grid fills whole waves of the GPU: the smallest split
     // count (at least two blocks' worth of work per SM) whose last wave is >= 95 % full.
     size_t splits = katsu_div_up(size_t(ctx->num_sms) * 2, out_tiles);
@@ -661,9 +726,10 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr
               nhwc_map(&mx, xt, n, h, wd, c, 8, 4, (int)stride, sw) &&
               nhwc_map(&mx_lo, three ? xt_lo : xt, n, h, wd, c, 8, 4, (int)stride, sw);
     if (!ok) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv dW)");
-    KATSU_CUDA_TRY(cudaFuncSetAttribute(conv_dw_igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-    dim3 grid((unsigned)(katsu_div_up(k, (size_t)BM) * katsu_div_up(c, (size_t)BN)), (unsigned)taps, (unsigned)splits);
-    KATSU_LAUNCH(ctx, conv_dw_igemm_kernel, grid, 192, kSmemBytes, mg, mg_lo, mx, mx_lo, p);
+    dim3 grid((unsigned)(katsu_div_up(k, (size_t)BM) * katsu_div_up(c, bnt)), (unsigned)taps, (unsigned)splits);
+    auto kernel = bnt == 32 ? conv_dw_igemm_kernel<32> : bnt == 64 ? conv_dw_igemm_kernel<64> : conv_dw_igemm_kernel<128>;
+    KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    KATSU_LAUNCH(ctx, kernel, grid, 192, kSmemBytes, mg, mg_lo, mx, mx_lo, p);
     KATSU_LAUNCH(ctx, dw_fold_kernel, (unsigned)katsu_div_up(k * c * taps, (size_t)256), 256, 0, p.partial, dw, (int)k,
                  (int)c, (int)taps, (int)splits, accumulate);
     return KATSU_OK;
