@@ -23,6 +23,9 @@ struct katsu_cuda_ctx {
     // it are serialised by stream order.
     float *scratch;
     size_t scratch_floats;
+    // set by conv2d_bwd while one call computes both dX and dW on the implicit-GEMM path: the dX
+    // launch stages g (channels-innermost copy) where the dW launch expects it, once for both
+    int share_g_staging, g_staged;
     // Buffer written by katsu_cuda_flush_l2.
     float *flush;
     size_t flush_floats;

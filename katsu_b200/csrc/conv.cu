@@ -67,6 +67,8 @@ extern "C" int32_t katsu_cuda_conv2d_bwd(katsu_cuda_ctx *ctx, const float *x, co
     KATSU_TRY(katsu_conv_stencil_bwd(ctx, x, w, gr, dx, dw, n, c, h, wd, k, r, s, stride, pad, accumulate,
                                      &handled));
     if (handled) return KATSU_OK;
+    ctx->share_g_staging = (dx != nullptr && dw != nullptr) ? 1 : 0;
+    ctx->g_staged = 0;
     if (dx != nullptr) {
         KATSU_TRY(katsu_conv_igemm_dx(ctx, w, gr, dx, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow, accumulate, &handled));
         if (!handled)
@@ -77,5 +79,6 @@ extern "C" int32_t katsu_cuda_conv2d_bwd(katsu_cuda_ctx *ctx, const float *x, co
         if (!handled)
             KATSU_TRY(katsu_conv_direct_dw(ctx, x, gr, dw, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow, accumulate));
     }
+    ctx->share_g_staging = ctx->g_staged = 0;
     return KATSU_OK;
 }

@@ -521,6 +521,35 @@ bool igemm_shape(const katsu_cuda_ctx *ctx, const Shape &g) {
     return katsu_tensor_map_encoder() != nullptr;
 }
 
+// Split of the dW contraction over pixel groups and the scratch it needs.
+struct DwPlan {
+    size_t bnt, splits, groups_per_split, partial_floats, scratch_floats;
+};
+
+DwPlan dw_plan(const katsu_cuda_ctx *ctx, const Shape &g) {
+    DwPlan plan;
+    const size_t taps = g.r * g.s;
+    const size_t total_groups = g.n * katsu_div_up(g.ow, 8) * katsu_div_up(g.oh, 4);
+    // channel-tile width of the c side: narrow layers get narrow MMAs and operand tiles
+    plan.bnt = g.c <= 32 ? 32 : g.c <= 64 ? 64 : 128;
+    const size_t out_tiles = katsu_div_up(g.k, (size_t)BM) * katsu_div_up(g.c, plan.bnt) * taps;
+    // Split the pixel range so that the grid fills whole waves of the GPU: the smallest split
+    // count (at least two blocks' worth of work per SM) whose last wave is >= 95 % full.
+    size_t splits = katsu_div_up(size_t(ctx->num_sms) * 2, out_tiles);
+    for (size_t cand = splits; cand < splits + size_t(ctx->num_sms); ++cand) {
+        const size_t blocks = out_tiles * cand, waves = katsu_div_up(blocks, (size_t)ctx->num_sms);
+        if (blocks * 100 >= waves * ctx->num_sms * 95) { splits = cand; break; }
+    }
+    if (splits > total_groups) splits = total_groups;
+    if (splits < 1) splits = 1;
+    plan.groups_per_split = katsu_div_up(total_groups, splits);
+    plan.splits = katsu_div_up(total_groups, plan.groups_per_split);
+    plan.partial_floats = plan.splits * taps * g.k * g.c;
+    const bool three = ctx->precision == KATSU_MODE_3XTF32;
+    plan.scratch_floats = (padded(g.n * g.c * g.h * g.w) + padded(g.n * g.k * g.oh * g.ow)) * (three ? 2 : 1) + padded(plan.partial_floats);
+    return plan;
+}
+
 // Forward / dX launch: picks the channel-tile width, builds the B maps for it and starts one
 // persistent block per SM (or per tile, if there are fewer).
 template <int BNT>
@@ -604,11 +633,16 @@ int32_t katsu_conv_igemm_dx(katsu_cuda_ctx *ctx, const float *w, const float *gr
     const bool three = ctx->precision == KATSU_MODE_3XTF32;
     const size_t ge = n * k * oh * ow, we = k * c * r * s, taps = r * s;
     float *base = nullptr;
-    KATSU_TRY(katsu_scratch(ctx, (padded(ge) + padded(we)) * (three ? 2 : 1), &base));
+    size_t need = (padded(ge) + padded(we)) * (three ? 2 : 1);
+    // a dW launch of the same backward call follows: size the scratch for it now, so that it is
+    // not reallocated in between and the staged g can be shared
+    if (ctx->share_g_staging) need = need > dw_plan(ctx, g).scratch_floats ? need : dw_plan(ctx, g).scratch_floats;
+    KATSU_TRY(katsu_scratch(ctx, need, &base));
     Scratch sc = {base, 0};
     float *gt = sc.take(ge), *gt_lo = three ? sc.take(ge) : nullptr;
     float *wb = sc.take(we), *wb_lo = three ? sc.take(we) : nullptr;
     KATSU_TRY(stage_nhwc(ctx, gr, gt, gt_lo, n, k, oh * ow));
+    if (ctx->share_g_staging) ctx->g_staged = 1;
     KATSU_LAUNCH(ctx, weights_to_taps_kernel, (unsigned)katsu_div_up(we, 256), 256, 0, w, (float *)nullptr,
                  (float *)nullptr, wb, wb_lo, (int)k, (int)c, (int)taps);
 
@@ -694,31 +728,18 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr
         p.off_y[t] = (short)((int)(t / s) - (int)pad);
         p.off_x[t] = (short)((int)(t % s) - (int)pad);
     }
-    const size_t total_groups = n * p.groups_x * p.groups_y;
-    // channel-tile width of the c side: narrow layers get narrow MMAs and operand tiles
-    const size_t bnt = c <= 32 ? 32 : c <= 64 ? 64 : 128;
-    const size_t out_tiles = katsu_div_up(k, (size_t)BM) * katsu_div_up(c, bnt) * taps;
-    // Split the pixel range so that the grid fills whole waves of the GPU: the smallest split
-    // count (at least two blocks' worth of work per SM) whose last wave is >= 95 % full.
-    size_t splits = katsu_div_up(size_t(ctx->num_sms) * 2, out_tiles);
-    for (size_t cand = splits; cand < splits + size_t(ctx->num_sms); ++cand) {
-        const size_t blocks = out_tiles * cand, waves = katsu_div_up(blocks, (size_t)ctx->num_sms);
-        if (blocks * 100 >= waves * ctx->num_sms * 95) { splits = cand; break; }
-    }
-    if (splits > total_groups) splits = total_groups;
-    if (splits < 1) splits = 1;
-    p.groups_per_split = (int)katsu_div_up(total_groups, splits);
-    splits = katsu_div_up(total_groups, (size_t)p.groups_per_split);
-
-    const size_t partial_e = splits * taps * k * c;
+    const DwPlan plan = dw_plan(ctx, g);
+    const size_t bnt = plan.bnt, splits = plan.splits;
+    p.groups_per_split = (int)plan.groups_per_split;
     float *base = nullptr;
-    KATSU_TRY(katsu_scratch(ctx, (padded(xe) + padded(ge)) * (three ? 2 : 1) + padded(partial_e), &base));
+    KATSU_TRY(katsu_scratch(ctx, plan.scratch_floats, &base));
+    // g first: a backward call that also computes dX has already staged it at the same place
     Scratch sc = {base, 0};
-    float *xt = sc.take(xe), *xt_lo = three ? sc.take(xe) : nullptr;
     float *gt = sc.take(ge), *gt_lo = three ? sc.take(ge) : nullptr;
-    p.partial = sc.take(partial_e);
+    float *xt = sc.take(xe), *xt_lo = three ? sc.take(xe) : nullptr;
+    p.partial = sc.take(plan.partial_floats);
     KATSU_TRY(stage_nhwc(ctx, x, xt, xt_lo, n, c, h * wd));
-    KATSU_TRY(stage_nhwc(ctx, gr, gt, gt_lo, n, k, oh * ow));
+    if (!ctx->g_staged) KATSU_TRY(stage_nhwc(ctx, gr, gt, gt_lo, n, k, oh * ow));
 
     CUtensorMap mg, mg_lo, mx, mx_lo;
     const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
