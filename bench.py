@@ -273,16 +273,22 @@ def run_ours(args):
     part_ms = {name: sum(v) / len(v) for name, v in parts.items()}
 
     # End to end through the C ABI with HOST buffers: pinned x in, dX and dW out, every step.
-    # The batch is cut into chunks that alternate between two contexts (streams) of the same
-    # device, so chunk i+1's host->device copy and chunk i-1's device->host copy overlap chunk
-    # i's kernels -- what a caller with a data loader does.  dW partials of the two contexts are
-    # added at the end (and all-reduced across ranks).
+    # The batch is cut into chunks that rotate over a few contexts (streams) of the same device:
+    # within one stream a chunk's copy in, kernels and copy out are serial, so it takes three or
+    # more streams to keep the two copy engines and the SMs busy at once -- what a caller with a
+    # data loader does.  The contexts' dW partials are added on the device (events order the
+    # other streams before the adds; the host does not
+    # block inside a step), all-reduced across ranks and copied to a pinned slot of that step;
+    # the host synchronises once after the last step, so consecutive steps pipeline as well.
     for p in (py, pg, pdx):
         ctx.free(p)
-    x_pin, dx_pin, dw_pin = ctx.pinned(x_count), ctx.pinned(x_count), ctx.pinned(w_count)
+    e2e_steps = max(3, min(args.steps, 10))
+    x_pin, dx_pin = ctx.pinned(x_count), ctx.pinned(x_count)
+    dw_pin = [ctx.pinned(w_count) for _ in range(e2e_steps + 1)]
     x_pin[:] = x_host
-    lanes = [ctx, cabi.Context(local_rank)]
-    n_chunks = min(8, n) if n >= 2 else 1
+    n_lanes = max(1, args.e2e_lanes)
+    lanes = [ctx] + [cabi.Context(local_rank) for _ in range(n_lanes - 1)]
+    n_chunks = max(1, min(args.e2e_chunks, n // 16))
     bounds = [dp.shard(n, i, n_chunks) for i in range(n_chunks)]
     per_img_x, per_img_y = c * h * wd, k * spec.oh * spec.ow
     chunk_max = max(cnt for _, cnt in bounds)
@@ -291,32 +297,45 @@ def run_ours(args):
         lane_buf.append({"w": lane_ctx.upload(w_host), "x": lane_ctx.alloc(chunk_max * per_img_x),
                          "y": lane_ctx.alloc(chunk_max * per_img_y), "g": lane_ctx.alloc(chunk_max * per_img_y),
                          "dx": lane_ctx.alloc(chunk_max * per_img_x), "dw": lane_ctx.alloc(w_count)})
+    lane_done = [lane_ctx.event() for lane_ctx in lanes]
 
-    def e2e_step():
+    def e2e_step(slot):
+        # the other lanes must not overwrite their dW partials before lane 0 has added the previous step's
+        for lane_ctx in lanes[1:]:
+            lane_ctx.wait_event(lane_done[0])
         for i, (first_img, cnt) in enumerate(bounds):
-            lane_ctx, b = lanes[i % 2], lane_buf[i % 2]
+            lane_ctx, b = lanes[i % n_lanes], lane_buf[i % n_lanes]
             cg = (cnt, c, h, wd, k, r, s, spec.stride, spec.pad)
             lane_ctx.h2d(b["x"], x_pin[first_img * per_img_x:(first_img + cnt) * per_img_x])
             lane_ctx.conv2d_fwd(b["x"], b["w"], b["y"], *cg)
             lane_ctx.call("katsu_cuda_add", b["y"], b["y"], b["g"], cnt * per_img_y)
-            lane_ctx.conv2d_bwd(b["x"], b["w"], b["g"], b["dx"], b["dw"], *cg, 1 if i >= 2 else 0)
+            lane_ctx.conv2d_bwd(b["x"], b["w"], b["g"], b["dx"], 0, *cg, 0)
+            lane_ctx.conv2d_bwd(b["x"], b["w"], b["g"], 0, b["dw"], *cg, 1 if i >= n_lanes else 0)
             lane_ctx.d2h_async(dx_pin[first_img * per_img_x:(first_img + cnt) * per_img_x], b["dx"])
-        lanes[1].sync()
-        if n_chunks > 1:
-            ctx.call("katsu_cuda_axpy_acc", lane_buf[0]["dw"], lane_buf[1]["dw"], w_count)
+        for j in range(1, min(n_lanes, n_chunks)):
+            lanes[j].record(lane_done[j])
+            ctx.wait_event(lane_done[j])
+            ctx.call("katsu_cuda_axpy_acc", lane_buf[0]["dw"], lane_buf[j]["dw"], w_count)
         if world > 1:
             ctx.call("katsu_cuda_allreduce_sum", lane_buf[0]["dw"], w_count)
-        ctx.d2h(dw_pin, lane_buf[0]["dw"])
+        ctx.d2h_async(dw_pin[slot], lane_buf[0]["dw"])
+        ctx.record(lane_done[0])
 
-    e2e_step()
+    ctx.record(lane_done[0])
+    e2e_step(e2e_steps)
+    for lane_ctx in lanes:
+        lane_ctx.sync()
     barrier()
-    e2e_steps = max(3, min(args.steps, 10))
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    ctx.sync()
+    for step_index in range(e2e_steps):
+        e2e_step(step_index)
+    for lane_ctx in lanes:
+        lane_ctx.sync()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
     barrier()
+    # every step's dW reached the host and is the same (same inputs every step)
+    if not all(np.array_equal(dw_pin[0], dw_pin[i]) for i in range(1, e2e_steps)):
+        raise RuntimeError("end-to-end leg: dW differs between steps")
 
     if dist is not None:
         import torch
@@ -363,7 +382,7 @@ def run_ours(args):
             "roofline": roof,
             "e2e": {"value": global_batch / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 4 * x_count, "d2h_bytes_per_step": 4 * (x_count + w_count),
-                    "pipeline": f"{n_chunks} batch chunks over 2 streams, pinned host buffers"},
+                    "pipeline": f"{n_chunks} batch chunks over {n_lanes} streams, pinned host buffers, one host sync after the last step"},
             "gpu_launches": launches,
             "clocks": clocks.summary(),
         }
@@ -376,9 +395,10 @@ def run_ours(args):
     for lane_ctx, b in zip(lanes, lane_buf):
         for p in b.values():
             lane_ctx.free(p)
-    for a in (x_pin, dx_pin, dw_pin):
+    for a in [x_pin, dx_pin] + dw_pin:
         ctx.free_pinned(a)
-    lanes[1].close()
+    for lane_ctx in lanes[1:]:
+        lane_ctx.close()
     if world > 1:
         ctx.call("katsu_cuda_comm_destroy")
         dist.destroy_process_group()
@@ -507,6 +527,8 @@ def main():
     ap.add_argument("--scaling", choices=["strong", "weak"], default="strong")
     ap.add_argument("--cpu-sample", type=int, default=32, help="images in the single-thread CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-chunks", type=int, default=16, help="batch chunks of the end-to-end leg (at least 16 images each)")
+    ap.add_argument("--e2e-lanes", type=int, default=4, help="contexts (streams) the chunks rotate over")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (small profiling cases)")
     args = ap.parse_args()
     if args.workload == "small_cnn":

@@ -175,6 +175,11 @@ int32_t katsu_cuda_event_record(katsu_cuda_ctx *ctx, katsu_cuda_event *event);
 int32_t katsu_cuda_event_elapsed_ms(katsu_cuda_ctx *ctx, katsu_cuda_event *start, katsu_cuda_event *stop,
                                     float *out_ms);
 int32_t katsu_cuda_event_destroy(katsu_cuda_ctx *ctx, katsu_cuda_event *event);
+/* Makes the work queued on `ctx` after this call wait, on the device, for everything that was
+ * queued before `event` was last recorded (on this or another context of the same device).
+ * The host does not block.  No counterpart in the reference (it has one thread and no queue);
+ * it lets two contexts pipeline batch chunks without a host synchronisation per step. */
+int32_t katsu_cuda_wait_event(katsu_cuda_ctx *ctx, katsu_cuda_event *event);
 /* Overwrites a private buffer larger than L2 so the next kernel starts cold. */
 int32_t katsu_cuda_flush_l2(katsu_cuda_ctx *ctx);
 

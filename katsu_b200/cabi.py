@@ -65,6 +65,7 @@ SIGNATURES = {
     "katsu_cuda_event_record": [_ctx, ctypes.c_void_p],
     "katsu_cuda_event_elapsed_ms": [_ctx, ctypes.c_void_p, ctypes.c_void_p, _c_float_p],
     "katsu_cuda_event_destroy": [_ctx, ctypes.c_void_p],
+    "katsu_cuda_wait_event": [_ctx, ctypes.c_void_p],
     "katsu_cuda_flush_l2": [_ctx],
     "katsu_cuda_selftest_wait_timeout": [_ctx, ctypes.c_uint64],
 }
@@ -205,6 +206,10 @@ class Context:
         out = ctypes.c_float()
         self.call("katsu_cuda_event_elapsed_ms", start, stop, ctypes.byref(out))
         return out.value
+
+    def wait_event(self, event: int) -> None:
+        """Device-side wait of this context's queue for `event` (recorded on any context of the device)."""
+        self.call("katsu_cuda_wait_event", event)
 
     def event_destroy(self, event: int) -> None:
         self.call("katsu_cuda_event_destroy", event)

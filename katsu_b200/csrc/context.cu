@@ -272,6 +272,13 @@ extern "C" int32_t katsu_cuda_event_record(katsu_cuda_ctx *ctx, katsu_cuda_event
     return KATSU_OK;
 }
 
+extern "C" int32_t katsu_cuda_wait_event(katsu_cuda_ctx *ctx, katsu_cuda_event *event) {
+    KATSU_REQUIRE(event != nullptr, "event is null");
+    KATSU_TRY(katsu_bind(ctx));
+    KATSU_CUDA_TRY(cudaStreamWaitEvent(ctx->stream, event->ev, 0));
+    return KATSU_OK;
+}
+
 extern "C" int32_t katsu_cuda_event_elapsed_ms(katsu_cuda_ctx *ctx, katsu_cuda_event *start,
                                                katsu_cuda_event *stop, float *out_ms) {
     KATSU_REQUIRE(start != nullptr && stop != nullptr && out_ms != nullptr, "null argument");
