@@ -7,14 +7,26 @@
 // Precision.  kind::tf32 truncates its f32 inputs to TF32.  TF32 mode issues one
 // MMA per k-step on the raw data.  3xTF32 mode restores FP32-grade accuracy with
 // the split x = hi + lo, hi = trunc_tf32(x) (what the hardware sees when given x),
-// lo = x - hi: three MMAs per k-step, hi*hi + lo*hi + hi*lo, into the same f32
-// accumulator.  The lo arrays are produced by a streaming pre-pass into scratch.
+// lo = x - hi: three MMAs per k-step, lo*hi + hi*lo + hi*hi, into the same f32
+// accumulator.
+//
+// Where the operands live.  With both operands in shared memory a 128x128x8 MMA reads 8 KiB
+// in its 64 pipe cycles -- the whole 128 B/clk of the SM's shared memory, before TMA has
+// written anything -- and every k-block pulled 64 KiB (hi and lo tiles of both operands)
+// through L2; that form topped out at 48 % of the pipe.  So A goes through TENSOR MEMORY: TMA drops the raw A tile in shared memory, four
+// builder warps (thread = tile row) read it once, compute lo on the fly and write hi | lo
+// with tcgen05.st; the MMAs then read only B (hi and lo tiles, lo produced by a streaming
+// pre-pass) from shared memory.  A needs no lo array in HBM at all and a k-block pulls 48 KiB.
+// Measured 8192^3: 193 TFLOP/s useful = 580 issued (3xTF32), 175 before.  What bounds it now is
+// L2 -> SM traffic of 128 x 128 tiles (about 9 TB/s aggregate at that rate); a 256-row tile
+// would halve the B traffic per MMA but leaves no tensor-memory columns for the A stages.
 //
 // Accumulation.  The tensor core's f32 accumulate loses a little on every k-step
-// (measured: relative error grows about linearly with K, 1.2e-6 at K = 512), so a
-// tile rotates its k-blocks over four TMEM accumulators that are added in f32 at
-// the end, and long K is split over blockIdx.z with an ordered fold of the
-// partial tiles (bit-reproducible, no atomics).
+// (measured: relative error grows about linearly with K, 1.2e-6 at K = 512), so k-blocks
+// alternate between two accumulators and every DRAIN k-blocks four epilogue warps fold both
+// into f32 registers (chains of at most 512 terms).  Split-K over blockIdx.z only fills the
+// GPU when there are fewer tiles than SMs; slabs are folded in a fixed order
+// (bit-reproducible, no atomics).
 #include "common.cuh"
 #include "sm100.cuh"
 
@@ -25,8 +37,9 @@ namespace {
 constexpr int BM = 128;      // tile rows == TMEM lanes
 constexpr int BN = 128;      // tile columns
 constexpr int BK = 32;       // f32 per 128-byte swizzle row
-constexpr int NACC = 4;      // rotating accumulators (4 x 128 columns = all of TMEM)
-constexpr int STAGES = 3;
+constexpr int AS = 4;          // shared-memory slots of the raw A tile (free as soon as the builders have read it)
+constexpr int BS = 4;          // shared-memory slots of the B tiles, hi | lo (free when the MMAs that read them are done)
+constexpr int TS = 4;          // tensor-memory stages of A, hi | lo
 constexpr int TILE_BYTES = BM * BK * 4;  // 16 KiB, same for A and B tiles (BM == BN)
 
 struct GemmParams {
@@ -47,36 +60,67 @@ __global__ void __launch_bounds__(256) split_lo_kernel(const float *__restrict__
     }
 }
 
+constexpr int DRAIN = 32;            // k-blocks per accumulator batch (2 accumulators x 16 k-blocks x 32)
+constexpr uint32_t A_COL0 = 2 * BN;  // TMEM: [2 accumulators x 128][TS A stages x {32 hi, 32 lo}]
+
+// Warps 0-3: drains and the epilogue (TMEM lane quarter = warp).  Warps 4-7: A builders
+// (quarter = warp & 3).  Warp 8: TMA loads of A.  Warp 9: MMA issue.  Warp 10: TMA loads of B.
+// A and B have separate rings because their slots live differently long: an A slot is free once
+// the builders have read it, a B slot only when the MMAs that read it have completed, and a
+// completion becomes visible ~300 cycles after issue with the refill another ~1000 behind.  With
+// one ring of four 48 KiB stages that round trip (~3000 cycles per slot) capped the pipe at 67 %.  (A second builder group and eight
+// drain warps were measured slower: 183 against 193 TFLOP/s at 8192^3; the kernel is bound by
+// L2 -> shared-memory traffic of its 128 x 128 tiles, not by the builders.)
+constexpr int RASTER_W = 16;
+constexpr int GEMM_THREADS = 11 * 32, TMA_A_WARP = 8, MMA_WARP = 9, TMA_B_WARP = 10;
+
 template <bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(128, 1)
-umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_lo,
-                 const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_b_lo,
-                 GemmParams p) {
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_b_lo, GemmParams p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    // stage layout: [A hi][A lo][B hi][B lo], 16 KiB each
-    __shared__ uint64_t full[STAGES], empty[STAGES], done;
+    __shared__ uint64_t a_full[AS], a_read[AS], b_full[BS], b_free[BS], t_free[TS], a_ready[TS], batch_done, drained;
     __shared__ uint32_t tmem_slot;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    // Tile order: bands of RASTER_W column tiles, row tiles fastest inside a band, so that the
+    // tiles in flight at one time (one per SM) share few distinct A and B panels and those stay
+    // in L2 (x-fastest order re-read all of B, hi and lo, for every 2-3 tile rows).
+    int tile_m, tile_n;
+    {
+        const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
+        const int band = blockIdx.x / (RASTER_W * m_tiles), within = blockIdx.x % (RASTER_W * m_tiles);
+        const int width = (n_tiles - band * RASTER_W) < RASTER_W ? (n_tiles - band * RASTER_W) : RASTER_W;
+        tile_n = band * RASTER_W + within % width;
+        tile_m = within / width;
+    }
+    const int m0 = tile_m * BM, n0 = tile_n * BN;
     const int kb_total = (p.K + BK - 1) / BK;
     const int kb_begin = blockIdx.z * p.kblocks_per_split;
     int kb_end = kb_begin + p.kblocks_per_split;
     if (kb_end > kb_total) kb_end = kb_total;
-    const int kblocks = kb_end - kb_begin;
-    const int tiles_per_stage = p.three_pass ? 4 : 2;
-    const uint32_t stage_bytes = 4 * TILE_BYTES;
+    const int kblocks = kb_end > kb_begin ? kb_end - kb_begin : 0;
+    const int batches = (kblocks + DRAIN - 1) / DRAIN;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], 1);
+        for (int s = 0; s < AS; ++s) {
+            mbar_init(&a_full[s], 1);
+            mbar_init(&a_read[s], 4);
         }
-        mbar_init(&done, 1);
+        for (int s = 0; s < BS; ++s) {
+            mbar_init(&b_full[s], 1);
+            mbar_init(&b_free[s], 1);
+        }
+        for (int s = 0; s < TS; ++s) {
+            mbar_init(&t_free[s], 1);
+            mbar_init(&a_ready[s], 4);
+        }
+        mbar_init(&batch_done, 1);
+        mbar_init(&drained, 4);
         mbar_init_fence();
     }
-    if (warp == 0) {
-        tmem_alloc(&tmem_slot, NACC * BN);
+    if (warp == MMA_WARP) {
+        tmem_alloc(&tmem_slot, 512);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -84,117 +128,170 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_slot;
 
-    if (warp == 0 && lane == 0) {
-        // ---- TMA producer ----
+    unsigned char *a_slots = smem, *b_slots = smem + AS * TILE_BYTES;
+    if (warp == TMA_A_WARP && lane == 0) {
+        // ---- TMA producer of A ----
         for (int i = 0; i < kblocks; ++i) {
-            const int s = i % STAGES;
-            if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, p.status, 11)) break;
-            mbar_arrive_expect_tx(&full[s], tiles_per_stage * TILE_BYTES);
-            unsigned char *st = smem + s * stage_bytes;
+            const int sa = i % AS;
+            if (i >= AS && !mbar_wait(&a_read[sa], ((i / AS) - 1) & 1, p.status, 11)) break;
+            mbar_arrive_expect_tx(&a_full[sa], TILE_BYTES);
+            unsigned char *ad = a_slots + sa * TILE_BYTES;
+            const int k0 = (kb_begin + i) * BK;
+            if (!A_MN) {
+                tma_load_2d(ad, &map_a, &a_full[sa], k0, m0);
+            } else {
+                for (int j = 0; j < BM / 32; ++j) tma_load_2d(ad + j * 4096, &map_a, &a_full[sa], m0 + 32 * j, k0);
+            }
+        }
+    } else if (warp == TMA_B_WARP && lane == 0) {
+        // ---- TMA producer of B (hi and lo tiles) ----
+        for (int i = 0; i < kblocks; ++i) {
+            const int sb = i % BS;
+            if (i >= BS && !mbar_wait(&b_free[sb], ((i / BS) - 1) & 1, p.status, 17)) break;
+            mbar_arrive_expect_tx(&b_full[sb], (p.three_pass ? 2 : 1) * TILE_BYTES);
+            unsigned char *bd = b_slots + sb * 2 * TILE_BYTES;
             const int k0 = (kb_begin + i) * BK;
             for (int part = 0; part < (p.three_pass ? 2 : 1); ++part) {
-                const CUtensorMap *ma = part ? &map_a_lo : &map_a;
                 const CUtensorMap *mb = part ? &map_b_lo : &map_b;
-                unsigned char *ad = st + part * TILE_BYTES, *bd = st + (2 + part) * TILE_BYTES;
-                if (!A_MN) {
-                    tma_load_2d(ad, ma, &full[s], k0, m0);
-                } else {
-                    for (int j = 0; j < BM / 32; ++j) tma_load_2d(ad + j * 4096, ma, &full[s], m0 + 32 * j, k0);
-                }
                 if (!B_MN) {
-                    tma_load_2d(bd, mb, &full[s], k0, n0);
+                    tma_load_2d(bd + part * TILE_BYTES, mb, &b_full[sb], k0, n0);
                 } else {
-                    for (int j = 0; j < BN / 32; ++j) tma_load_2d(bd + j * 4096, mb, &full[s], n0 + 32 * j, k0);
+                    for (int j = 0; j < BN / 32; ++j) tma_load_2d(bd + part * TILE_BYTES + j * 4096, mb, &b_full[sb], n0 + 32 * j, k0);
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---- MMA issuer: the whole warp runs the loop, the thread chosen by elect.sync issues.
-        // With warp-uniform control flow the operands stay in uniform registers, and a wait on
-        // an already-full stage costs ~90 cycles instead of ~300 behind a lane == 0 branch
-        // (measured); at 768 tensor-pipe cycles per 3xTF32 k-block that is the difference
-        // between ~70 % and ~90 % of the pipe. ----
-        const bool issue = elect_one();
-        const uint32_t idesc = idesc_tf32(BM, BN, A_MN, B_MN);
+    } else if (warp >= 4 && warp < 8) {
+        // ---- A builders: thread = one row of the tile; hi goes in raw (the tensor core truncates) ----
+        const int quarter = warp & 3, row = quarter * 32 + lane;
+        const uint32_t lane_addr = tmem_base + (uint32_t(quarter * 32) << 16) + A_COL0;
         for (int i = 0; i < kblocks; ++i) {
-            const int s = i % STAGES;
-            if (!mbar_wait_warp_ready(&full[s], (i / STAGES) & 1, p.status, 12)) break;
-            tc_fence_after_sync();
-            const uint32_t st = smem_u32(smem + s * stage_bytes);
-            const uint32_t acc = tmem_base + uint32_t(i % NACC) * BN;
-            const bool first = i < NACC;
-            if (issue) {
+            const int sa = i % AS, s = i % TS;
+            if (!mbar_wait_warp_ready(&a_full[sa], (i / AS) & 1, p.status, 14)) break;
+            const unsigned char *ad = a_slots + sa * TILE_BYTES;
+            float v[32];
+            if (!A_MN) {
+                // K-major tile, 128-byte-swizzled rows: chunk c of row r sits at chunk c ^ (r & 7)
 #pragma unroll
-                for (int j = 0; j < BK / 8; ++j) {
-                    const uint32_t a_off = A_MN ? j * 1024 : j * 32, b_off = B_MN ? j * 1024 : j * 32;
-                    auto desc = [&](uint32_t addr, bool mn) {
-                        return mn ? smem_desc(addr, 4096, 512, kLayoutSw128Base32) : smem_desc(addr, 16, 1024, kLayoutSw128);
-                    };
-                    const uint64_t a_hi = desc(st + a_off, A_MN), b_hi = desc(st + 2 * TILE_BYTES + b_off, B_MN);
-                    if (p.three_pass) {
-                        const uint64_t a_lo = desc(st + TILE_BYTES + a_off, A_MN);
-                        const uint64_t b_lo = desc(st + 3 * TILE_BYTES + b_off, B_MN);
-                        mma_tf32(acc, a_lo, b_hi, idesc, !(first && j == 0));
-                        mma_tf32(acc, a_hi, b_lo, idesc, true);
-                        mma_tf32(acc, a_hi, b_hi, idesc, true);
-                    } else {
-                        mma_tf32(acc, a_hi, b_hi, idesc, !(first && j == 0));
+                for (int c = 0; c < 8; ++c) {
+                    const float4 q = ld_shared_v4(ad + row * 128 + ((c ^ (row & 7)) << 4));
+                    v[4 * c] = q.x; v[4 * c + 1] = q.y; v[4 * c + 2] = q.z; v[4 * c + 3] = q.w;
+                }
+            } else {
+                // MN-major tile: four dense [32 k][32 m] sub-tiles; a warp reads one 128-byte k-row per load
+#pragma unroll
+                for (int k = 0; k < 32; ++k) v[k] = ld_shared_f32(ad + quarter * 4096 + k * 128 + lane * 4);
+            }
+            mbar_arrive_warp(&a_read[sa]);
+            if (i >= TS && !mbar_wait_warp_ready(&t_free[s], ((i / TS) - 1) & 1, p.status, 15)) break;
+            tc_fence_after_sync();
+            tmem_st_32x32(lane_addr + uint32_t(s) * 64, v);
+            if (p.three_pass) {
+#pragma unroll
+                for (int t = 0; t < 32; ++t) v[t] -= __uint_as_float(__float_as_uint(v[t]) & 0xFFFFE000u);
+                tmem_st_32x32(lane_addr + uint32_t(s) * 64 + 32, v);
+            }
+            tmem_st_wait();
+            tc_fence_before_sync();
+            mbar_arrive_warp(&a_ready[s]);
+        }
+    } else if (warp == MMA_WARP) {
+        // ---- MMA issue: the whole warp runs the loop, the thread chosen by elect.sync issues ----
+        const bool issue = elect_one();
+        const uint32_t idesc = idesc_tf32(BM, BN, false, B_MN);
+        bool ok = true;
+        for (int b = 0; b < batches && ok; ++b) {
+            // the previous batch's accumulators must have been folded into registers
+            if (b > 0 && !mbar_wait_warp(&drained, (b - 1) & 1, p.status, 16)) break;
+            tc_fence_after_sync();
+            const int i_end = (b + 1) * DRAIN < kblocks ? (b + 1) * DRAIN : kblocks;
+            for (int i = b * DRAIN; i < i_end; ++i) {
+                const int s = i % TS, sb = i % BS;
+                if (!mbar_wait_warp_ready(&a_ready[s], (i / TS) & 1, p.status, 12)) { ok = false; break; }
+                if (!mbar_wait_warp_ready(&b_full[sb], (i / BS) & 1, p.status, 18)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t bd = smem_u32(b_slots + sb * 2 * TILE_BYTES);
+                const int li = i - b * DRAIN;
+                const uint32_t acc = tmem_base + uint32_t(li & 1) * BN;
+                const uint32_t a_hi = tmem_base + A_COL0 + uint32_t(s) * 64, a_lo = a_hi + 32;
+                if (issue) {
+#pragma unroll
+                    for (int j = 0; j < BK / 8; ++j) {
+                        const uint32_t b_off = B_MN ? j * 1024 : j * 32;
+                        const uint64_t b_hi = B_MN ? smem_desc(bd + b_off, 4096, 512, kLayoutSw128Base32)
+                                                   : smem_desc(bd + b_off, 16, 1024, kLayoutSw128);
+                        const bool acc_flag = !(li < 2 && j == 0);
+                        if (p.three_pass) {
+                            const uint64_t b_lo = B_MN ? smem_desc(bd + TILE_BYTES + b_off, 4096, 512, kLayoutSw128Base32)
+                                                       : smem_desc(bd + TILE_BYTES + b_off, 16, 1024, kLayoutSw128);
+                            mma_tf32_ts(acc, a_lo + 8 * j, b_hi, idesc, acc_flag);
+                            mma_tf32_ts(acc, a_hi + 8 * j, b_lo, idesc, true);
+                            mma_tf32_ts(acc, a_hi + 8 * j, b_hi, idesc, true);
+                        } else {
+                            mma_tf32_ts(acc, a_hi + 8 * j, b_hi, idesc, acc_flag);
+                        }
+                    }
+                    mma_commit(&t_free[s]);
+                    mma_commit(&b_free[sb]);
+                    if (i == i_end - 1) mma_commit(&batch_done);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp < 4) {
+        // ---- drains and epilogue: warp w owns tile rows 32w .. 32w+31 ----
+        float run[BN];
+#pragma unroll
+        for (int i = 0; i < BN; ++i) run[i] = 0.f;
+        bool alive = true;
+        for (int b = 0; b < batches && alive; ++b) {
+            alive = mbar_wait_warp(&batch_done, b & 1, p.status, 13);
+            tc_fence_after_sync();
+            if (alive) {
+                const int in_batch = (kblocks - b * DRAIN) < DRAIN ? (kblocks - b * DRAIN) : DRAIN;
+#pragma unroll
+                for (int q = 0; q < BN / 32; ++q) {
+                    if (n0 + q * 32 >= p.N) break;  // warp-uniform
+                    for (int a = 0; a < 2 && a < in_batch; ++a) {
+                        float t[32];
+                        tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + a * BN + q * 32, t);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) run[q * 32 + i] += t[i];
                     }
                 }
-                mma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+                tc_fence_before_sync();
+                mbar_arrive_warp(&drained);
             }
-            __syncwarp();
         }
-        if (issue) mma_commit(&done);
-    }
-    __syncwarp();
-
-    // ---- epilogue: warp w owns tile rows 32w .. 32w+31 ----
-    const bool finished = mbar_wait(&done, 0, p.status, 13);
-    tc_fence_after_sync();
-    if (finished && kblocks > 0) {
         const int row = m0 + warp * 32 + lane;
-        const int used_acc = kblocks < NACC ? kblocks : NACC;
-        float *out = p.c + (p.splits > 1 ? size_t(blockIdx.z) * p.M * p.N : 0);
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-            if (n0 + c0 >= p.N) break;  // warp-uniform
-            float v[32];
-            tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + c0, v);
-            for (int a = 1; a < used_acc; ++a) {
-                float t[32];
-                tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + a * BN + c0, t);
+        if (alive && row < p.M) {
+            float *out = p.c + (p.splits > 1 ? size_t(blockIdx.z) * p.M * p.N : 0);
+            const bool acc_out = p.accumulate && p.splits == 1;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] += t[i];
-            }
-            if (row < p.M) {
+            for (int q = 0; q < BN / 32; ++q) {
+                const int c0 = q * 32;
+                if (n0 + c0 >= p.N) break;
                 float *dst = out + size_t(row) * p.N + n0 + c0;
-                const bool acc_out = p.accumulate && p.splits == 1;
                 if (n0 + c0 + 32 <= p.N && (p.N & 3) == 0) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
-                        float4 q = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                        float4 o = make_float4(run[c0 + i], run[c0 + i + 1], run[c0 + i + 2], run[c0 + i + 3]);
                         if (acc_out) {
-                            const float4 o = *reinterpret_cast<const float4 *>(dst + i);
-                            q.x += o.x; q.y += o.y; q.z += o.z; q.w += o.w;
+                            const float4 old = *reinterpret_cast<const float4 *>(dst + i);
+                            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
                         }
-                        *reinterpret_cast<float4 *>(dst + i) = q;
+                        *reinterpret_cast<float4 *>(dst + i) = o;
                     }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (n0 + c0 + i < p.N) dst[i] = acc_out ? dst[i] + v[i] : v[i];
+                        if (n0 + c0 + i < p.N) dst[i] = acc_out ? dst[i] + run[c0 + i] : run[c0 + i];
                 }
             }
         }
-    } else if (finished && kblocks == 0 && p.splits > 1) {
-        // an empty K range still owns a partial slab: it must read as zero
-        const int row = m0 + warp * 32 + lane;
-        if (row < p.M)
-            for (int c = n0; c < n0 + BN && c < p.N; ++c) p.c[(size_t(blockIdx.z) * p.M + row) * p.N + c] = 0.f;
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem_base, NACC * BN);
+    if (warp == MMA_WARP) tmem_dealloc(tmem_base, 512);
 }
 
 __global__ void __launch_bounds__(256)
@@ -221,41 +318,45 @@ bool operand_map(CUtensorMap *map, const float *base, bool mn_major, size_t mn_e
     return katsu_make_tensor_map(map, base, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
 }
 
+// MN-major A is read by the builder threads, not by the tensor core: dense 32 x 32 boxes.
+bool builder_map_mn(CUtensorMap *map, const float *base, size_t mn_extent, size_t k_extent) {
+    const uint64_t dims[2] = {mn_extent, k_extent}, strides[2] = {1, mn_extent};
+    const uint32_t box[2] = {32, BK};
+    return katsu_make_tensor_map(map, base, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
 template <bool A_MN, bool B_MN>
 int32_t launch(katsu_cuda_ctx *ctx, const float *a, const float *b, float *c, size_t M, size_t N, size_t K,
                int accumulate) {
     const bool three_pass = ctx->precision == KATSU_MODE_3XTF32;
-    const size_t a_count = M * K, b_count = K * N;
+    const size_t b_count = K * N;
     const int kb_total = (int)katsu_div_up(K, (size_t)BK);
-    // K split: keep each accumulator's chain short (<= 16 k-blocks = 512 terms) and fill the GPU.
+    // K split only to fill the GPU when there are fewer tiles than SMs (chains are kept short by
+    // the in-kernel drains); every split gets at least DRAIN k-blocks.
     const size_t tiles = katsu_div_up(M, (size_t)BM) * katsu_div_up(N, (size_t)BN);
-    int splits = (int)katsu_div_up((size_t)kb_total, (size_t)(NACC * 16));
-    const int fill = (int)katsu_div_up((size_t)ctx->num_sms, tiles);
-    if (splits < fill) splits = fill;
-    if (splits > kb_total) splits = kb_total;
+    int splits = (int)katsu_div_up((size_t)ctx->num_sms, tiles);
+    if (splits > kb_total / DRAIN) splits = kb_total / DRAIN;
+    if (splits < 1) splits = 1;
     if (splits > 1024) splits = 1024;
     int kb_per_split = (int)katsu_div_up((size_t)kb_total, (size_t)splits);
     splits = (int)katsu_div_up((size_t)kb_total, (size_t)kb_per_split);
 
-    size_t scratch_floats = (three_pass ? a_count + b_count : 0) + (splits > 1 ? size_t(splits) * M * N : 0);
+    size_t scratch_floats = (three_pass ? b_count : 0) + (splits > 1 ? size_t(splits) * M * N : 0);
     float *scratch = nullptr;
     if (scratch_floats) KATSU_TRY(katsu_scratch(ctx, scratch_floats + 64, &scratch));
-    float *a_lo = nullptr, *b_lo = nullptr, *slabs = nullptr;
+    float *b_lo = nullptr, *slabs = nullptr;
     size_t cursor = 0;
     auto take = [&](size_t n) { float *ptr = scratch + cursor; cursor += (n + 31) / 32 * 32; return ptr; };
     if (three_pass) {
-        a_lo = take(a_count);
         b_lo = take(b_count);
         const unsigned blocks = (unsigned)(size_t(ctx->num_sms) * 8);
-        KATSU_LAUNCH(ctx, split_lo_kernel, blocks, 256, 0, a, a_lo, a_count);
         KATSU_LAUNCH(ctx, split_lo_kernel, blocks, 256, 0, b, b_lo, b_count);
     }
     if (splits > 1) slabs = take(size_t(splits) * M * N);
 
-    CUtensorMap map_a, map_a_lo, map_b, map_b_lo;
-    bool ok = operand_map(&map_a, a, A_MN, M, K) && operand_map(&map_b, b, B_MN, N, K);
-    ok = ok && operand_map(&map_a_lo, three_pass ? a_lo : a, A_MN, M, K) &&
-         operand_map(&map_b_lo, three_pass ? b_lo : b, B_MN, N, K);
+    CUtensorMap map_a, map_b, map_b_lo;
+    bool ok = (A_MN ? builder_map_mn(&map_a, a, M, K) : operand_map(&map_a, a, false, M, K)) &&
+              operand_map(&map_b, b, B_MN, N, K) && operand_map(&map_b_lo, three_pass ? b_lo : b, B_MN, N, K);
     if (!ok) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed for a matmul operand");
 
     GemmParams p;
@@ -266,11 +367,11 @@ int32_t launch(katsu_cuda_ctx *ctx, const float *a, const float *b, float *c, si
     p.accumulate = accumulate;
     p.three_pass = three_pass ? 1 : 0;
     p.status = ctx->status;
-    const size_t smem = size_t(STAGES) * 4 * TILE_BYTES + 1024;
+    const size_t smem = size_t(AS + 2 * BS) * TILE_BYTES + 1024;
     auto kernel = umma_gemm_kernel<A_MN, B_MN>;
     KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid((unsigned)katsu_div_up(N, (size_t)BN), (unsigned)katsu_div_up(M, (size_t)BM), (unsigned)splits);
-    KATSU_LAUNCH(ctx, kernel, grid, 128, smem, map_a, map_a_lo, map_b, map_b_lo, p);
+    dim3 grid((unsigned)(katsu_div_up(N, (size_t)BN) * katsu_div_up(M, (size_t)BM)), 1, (unsigned)splits);
+    KATSU_LAUNCH(ctx, kernel, grid, GEMM_THREADS, smem, map_a, map_b, map_b_lo, p);
     if (splits > 1)
         KATSU_LAUNCH(ctx, fold_slabs_kernel, (unsigned)katsu_div_up(M * N, (size_t)256), 256, 0, slabs, c, M * N, splits,
                      accumulate);
