@@ -17,9 +17,9 @@
 // builder warps (thread = tile row) read it once, compute lo on the fly and write hi | lo
 // with tcgen05.st; the MMAs then read only B (hi and lo tiles, lo produced by a streaming
 // pre-pass) from shared memory.  A needs no lo array in HBM at all and a k-block pulls 48 KiB.
-// Measured 8192^3: 193 TFLOP/s useful = 580 issued (3xTF32), 175 before.  What bounds it now is
-// L2 -> SM traffic of 128 x 128 tiles (about 9 TB/s aggregate at that rate); a 256-row tile
-// would halve the B traffic per MMA but leaves no tensor-memory columns for the A stages.
+// Measured 8192^3: 203 TFLOP/s useful = 608 issued (3xTF32), 175 before.  No pipe is saturated at
+// that point (tensor 67 %, L2 38 %, DRAM 20 % at 4096^3): the hand-off ring bounds it.  A 256-row
+// tile would halve the B traffic per MMA but leaves no tensor-memory columns for the A stages.
 //
 // Accumulation.  The tensor core's f32 accumulate loses a little on every k-step
 // (measured: relative error grows about linearly with K, 1.2e-6 at K = 512), so k-blocks
