@@ -301,10 +301,15 @@ void Tensor::backward() const {
 namespace {
 
 using Pending = std::unordered_map<const TensorNode *, std::shared_ptr<DeviceBuffer>>;
+// Parents whose pending adjoint has received a contribution in this pass.  A pending adjoint
+// starts as zeros, so the first contribution of a convolution or matmul VJP may overwrite it
+// (0 + v == v) instead of reading it back: the read-modify-write epilogue of the strided dX
+// launches was four times slower than the plain store.
+using Touched = std::unordered_set<const TensorNode *>;
 
 // Op::backward, tensor.rs:365-449: adds this node's contribution to the
 // pending adjoint of each parent.
-void op_backward(const Tensor &node, const float *g, Pending &pending) {
+void op_backward(const Tensor &node, const float *g, Pending &pending, Touched &touched) {
     katsu_cuda_ctx *ctx = device_context();
     const Op op = node.op();
     const auto &parents = node.parents();
@@ -316,9 +321,19 @@ void op_backward(const Tensor &node, const float *g, Pending &pending) {
             const auto &xs = x.shape(), &ws = w.shape();
             float *px = pending.at(x.id())->ptr, *pw = pending.at(w.id())->ptr;
             if (x.id() != w.id()) {
-                // backward_buffers + `pending[parent] += grad` (tensor.rs:374-390) in one call
-                check(katsu_cuda_conv2d_bwd(ctx, x.device_data(), w.device_data(), g, px, pw, xs[0], xs[1], xs[2],
-                                            xs[3], ws[0], ws[2], ws[3], op.stride, op.padding, 1));
+                // backward_buffers + `pending[parent] += grad` (tensor.rs:374-390)
+                const int acc_x = touched.count(x.id()) ? 1 : 0, acc_w = touched.count(w.id()) ? 1 : 0;
+                if (acc_x == acc_w) {
+                    check(katsu_cuda_conv2d_bwd(ctx, x.device_data(), w.device_data(), g, px, pw, xs[0], xs[1], xs[2],
+                                                xs[3], ws[0], ws[2], ws[3], op.stride, op.padding, acc_x));
+                } else {
+                    check(katsu_cuda_conv2d_bwd(ctx, x.device_data(), w.device_data(), g, px, nullptr, xs[0], xs[1],
+                                                xs[2], xs[3], ws[0], ws[2], ws[3], op.stride, op.padding, acc_x));
+                    check(katsu_cuda_conv2d_bwd(ctx, x.device_data(), w.device_data(), g, nullptr, pw, xs[0], xs[1],
+                                                xs[2], xs[3], ws[0], ws[2], ws[3], op.stride, op.padding, acc_w));
+                }
+                touched.insert(x.id());
+                touched.insert(w.id());
             } else {
                 // Same node on both edges: sequential adds into one adjoint (tests/conv2d.rs:109-116).
                 DeviceBuffer dx(x.numel()), dw(w.numel());
@@ -327,6 +342,7 @@ void op_backward(const Tensor &node, const float *g, Pending &pending) {
                 check(katsu_cuda_axpy_acc(ctx, px, dx.ptr, x.numel()));
                 check(katsu_cuda_axpy_acc(ctx, pw, dw.ptr, w.numel()));
                 check(katsu_cuda_sync(ctx));
+                touched.insert(x.id());
             }
             return;
         }
@@ -340,13 +356,16 @@ void op_backward(const Tensor &node, const float *g, Pending &pending) {
                     check(katsu_cuda_axpy_acc(ctx, target, g, node.numel()));
                 else
                     check(katsu_cuda_mul_acc(ctx, target, g, other.device_data(), node.numel()));
+                touched.insert(parent.id());
             }
             return;
         case Op::Sum:
             check(katsu_cuda_bcast_acc(ctx, pending.at(parents[0].id())->ptr, g, parents[0].numel()));
+            touched.insert(parents[0].id());
             return;
         case Op::Reshape:
             check(katsu_cuda_axpy_acc(ctx, pending.at(parents[0].id())->ptr, g, node.numel()));
+            touched.insert(parents[0].id());
             return;
         case Op::Matmul: {
             const Tensor &a = parents[0], &b = parents[1];
@@ -354,11 +373,19 @@ void op_backward(const Tensor &node, const float *g, Pending &pending) {
             if (node.numel() == 0 || k == 0) return;  // tensor.rs:421-423
             float *pa = pending.at(a.id())->ptr, *pb = pending.at(b.id())->ptr;
             if (a.id() != b.id()) {
-                check(katsu_cuda_matmul_bwd(ctx, a.device_data(), b.device_data(), g, pa, pb, m, k, n, 1));
+                const int acc_a = touched.count(a.id()) ? 1 : 0, acc_b = touched.count(b.id()) ? 1 : 0;
+                if (acc_a == acc_b) {
+                    check(katsu_cuda_matmul_bwd(ctx, a.device_data(), b.device_data(), g, pa, pb, m, k, n, acc_a));
+                } else {
+                    check(katsu_cuda_matmul_bwd(ctx, a.device_data(), b.device_data(), g, pa, nullptr, m, k, n, acc_a));
+                    check(katsu_cuda_matmul_bwd(ctx, a.device_data(), b.device_data(), g, nullptr, pb, m, k, n, acc_b));
+                }
             } else {
                 check(katsu_cuda_matmul_bwd(ctx, a.device_data(), b.device_data(), g, pa, nullptr, m, k, n, 1));
                 check(katsu_cuda_matmul_bwd(ctx, a.device_data(), b.device_data(), g, nullptr, pb, m, k, n, 1));
             }
+            touched.insert(a.id());
+            touched.insert(b.id());
             return;
         }
     }
@@ -377,7 +404,9 @@ void Tensor::backward_with(const std::vector<float> &seed) const {
         check(katsu_cuda_h2d(ctx, pending.at(id())->ptr, seed.data(), numel()));
         check(katsu_cuda_sync(ctx));  // `seed` may be a temporary
     }
-    for (auto it = order.rbegin(); it != order.rend(); ++it) op_backward(*it, pending.at(it->id())->ptr, pending);
+    Touched touched;
+    touched.insert(id());  // the seed
+    for (auto it = order.rbegin(); it != order.rend(); ++it) op_backward(*it, pending.at(it->id())->ptr, pending, touched);
     // All borrows are validated before any gradient changes (tensor.rs:341-350).
     for (const Tensor &node : order)
         if (node.node()->borrows != 0) fail(ErrorKind::GradientBorrowed);
