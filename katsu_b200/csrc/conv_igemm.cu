@@ -440,6 +440,172 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
     if (warp == 4) tmem_dealloc(tmem_base, NACC * BNT);
 }
 
+// ---- dW for narrow layers (C <= 32): all taps in one block ---------------------------------
+// The kernel above gives every tap its own blocks, so the g tile (the larger operand when C is
+// small) is fetched and read by the MMAs once per tap.  Here one block holds g once per 32-pixel
+// k-block and the x tiles of ALL taps side by side along N (tap t occupies accumulator columns
+// 32 t .. 32 t + 31), so one MMA per k-step covers up to eight taps.  The accumulators (taps x 32
+// columns) leave no room for a second set, so a block works in chunks of CHUNK k-blocks (512
+// pixels, the longest accumulation chain): after a chunk the four epilogue warps write the
+// accumulators as that chunk's partial dW and the fold kernel adds the chunks in order.
+constexpr int TAPS_MAX = 16;   // taps x 32 accumulator columns <= 512
+constexpr int CHUNK = 16;      // k-blocks per chunk
+constexpr int TAPS_STAGES = 2;
+
+struct DwTapsParams {
+    float *partial;             // [chunks][taps][K][C]
+    int n_img, k, c, taps;
+    int groups_x, groups_y;     // 8 x 4 pixel groups over the output plane
+    long long total_groups;
+    int chunks;
+    int stride;
+    int three_pass;
+    int a_groups;               // 32-channel groups of g that exist (ceil(k / 32))
+    int *status;
+    short off_y[TAPS_MAX], off_x[TAPS_MAX];
+};
+
+__global__ void __launch_bounds__(192, 1)
+conv_dw_taps_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_g_lo,
+                    const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_x_lo,
+                    const __grid_constant__ DwTapsParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t full[TAPS_STAGES], empty[TAPS_STAGES], acc_full, acc_empty;
+    __shared__ uint32_t tmem_slot;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int groups_per_img = p.groups_x * p.groups_y;
+    const int parts = p.three_pass ? 2 : 1;
+    // stage: g hi | g lo (4 groups x 4 KiB each) | x hi per tap | x lo per tap
+    const uint32_t a_bytes = TILE_BYTES, b_bytes = uint32_t(p.taps) * 4096;
+    const uint32_t stage_bytes = 2 * a_bytes + 2 * b_bytes;
+    const int my_chunks = (p.chunks - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    uint32_t tmem_cols = 32;
+    while ((int)tmem_cols < p.taps * 32) tmem_cols <<= 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TAPS_STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(&acc_full, 1);
+        mbar_init(&acc_empty, 4);
+        mbar_init_fence();
+    }
+    if (warp == 5) {
+        tmem_alloc(&tmem_slot, tmem_cols);
+        tmem_relinquish();
+    }
+    // g groups beyond the layer's channels are never loaded: they must hold finite values
+    for (uint32_t i = threadIdx.x; i < TAPS_STAGES * stage_bytes / 16; i += blockDim.x)
+        st_shared_v4(smem + i * 16, make_float4(0.f, 0.f, 0.f, 0.f));
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_slot;
+
+    auto chunk_kblocks = [&](int chunk) {
+        const long long first = (long long)chunk * CHUNK;
+        const long long left = p.total_groups - first;
+        return int(left < CHUNK ? left : CHUNK);
+    };
+
+    if (warp == 4 && lane == 0) {
+        // ---- TMA producer ----
+        int g = 0;
+        bool ok = true;
+        for (int it = 0; it < my_chunks && ok; ++it) {
+            const int chunk = blockIdx.x + it * gridDim.x, nkb = chunk_kblocks(chunk);
+            for (int i = 0; i < nkb; ++i, ++g) {
+                const int s = g % TAPS_STAGES;
+                if (g >= TAPS_STAGES && !mbar_wait(&empty[s], ((g / TAPS_STAGES) - 1) & 1, p.status, 35)) { ok = false; break; }
+                mbar_arrive_expect_tx(&full[s], parts * (p.a_groups * 4096 + p.taps * 4096));
+                unsigned char *st = smem + s * stage_bytes;
+                const long long gidx = (long long)chunk * CHUNK + i;
+                const int img = int(gidx / groups_per_img);
+                const int r = int(gidx % groups_per_img);
+                const int oy0 = (r / p.groups_x) * 4, ox0 = (r % p.groups_x) * 8;
+                for (int part = 0; part < parts; ++part) {
+                    const CUtensorMap *mg = part ? &map_g_lo : &map_g;
+                    const CUtensorMap *mx = part ? &map_x_lo : &map_x;
+                    for (int j = 0; j < p.a_groups; ++j)
+                        tma_load_4d(st + part * a_bytes + j * 4096, mg, &full[s], 32 * j, ox0, oy0, img);
+                    for (int t = 0; t < p.taps; ++t)
+                        tma_load_4d(st + 2 * a_bytes + part * b_bytes + t * 4096, mx, &full[s], 0,
+                                    ox0 * p.stride + p.off_x[t], oy0 * p.stride + p.off_y[t], img);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ---- MMA issue: one MMA per k-step and pass covers up to eight taps (N = 256) ----
+        const bool issue = elect_one();
+        int g = 0;
+        bool ok = true;
+        for (int it = 0; it < my_chunks && ok; ++it) {
+            const int chunk = blockIdx.x + it * gridDim.x, nkb = chunk_kblocks(chunk);
+            if (it >= 1 && !mbar_wait_warp(&acc_empty, (it - 1) & 1, p.status, 36)) break;
+            tc_fence_after_sync();
+            for (int i = 0; i < nkb; ++i, ++g) {
+                const int s = g % TAPS_STAGES;
+                if (!mbar_wait_warp_ready(&full[s], (g / TAPS_STAGES) & 1, p.status, 37)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t st = smem_u32(smem + s * stage_bytes);
+                if (issue) {
+                    for (int t0 = 0; t0 < p.taps; t0 += 8) {
+                        const int nt = (p.taps - t0) < 8 ? (p.taps - t0) : 8;
+                        const uint32_t idesc = idesc_tf32(BM, nt * 32, true, true);
+                        const uint32_t acc = tmem_base + uint32_t(t0) * 32;
+#pragma unroll
+                        for (int j = 0; j < BK / 8; ++j) {
+                            const uint64_t a_hi = smem_desc(st + j * 1024, 4096, 512, kLayoutSw128Base32);
+                            const uint64_t b_hi = smem_desc(st + 2 * a_bytes + t0 * 4096 + j * 1024, 4096, 512, kLayoutSw128Base32);
+                            const bool acc_flag = !(i == 0 && j == 0);
+                            if (p.three_pass) {
+                                const uint64_t a_lo = smem_desc(st + a_bytes + j * 1024, 4096, 512, kLayoutSw128Base32);
+                                const uint64_t b_lo = smem_desc(st + 2 * a_bytes + b_bytes + t0 * 4096 + j * 1024, 4096, 512, kLayoutSw128Base32);
+                                mma_tf32(acc, a_lo, b_hi, idesc, acc_flag);
+                                mma_tf32(acc, a_hi, b_lo, idesc, true);
+                                mma_tf32(acc, a_hi, b_hi, idesc, true);
+                            } else {
+                                mma_tf32(acc, a_hi, b_hi, idesc, acc_flag);
+                            }
+                        }
+                    }
+                    mma_commit(&empty[s]);
+                    if (i == nkb - 1) mma_commit(&acc_full);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp < 4) {
+        // ---- epilogue: this chunk's accumulators become its partial dW (thread = oc) ----
+        const int oc = warp * 32 + lane;
+        for (int it = 0; it < my_chunks; ++it) {
+            const int chunk = blockIdx.x + it * gridDim.x;
+            if (!mbar_wait_warp(&acc_full, it & 1, p.status, 38)) break;
+            tc_fence_after_sync();
+            for (int t = 0; t < p.taps; ++t) {
+                float v[32];
+                tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + uint32_t(t) * 32, v);
+                if (t == p.taps - 1) {
+                    tc_fence_before_sync();
+                    mbar_arrive_warp(&acc_empty);
+                }
+                if (oc < p.k) {
+                    float *dst = p.partial + ((size_t(chunk) * p.taps + t) * p.k + oc) * p.c;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        if (i < p.c) *reinterpret_cast<float4 *>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tmem_base, tmem_cols);
+}
+
 // dw[k][c][tap] (+)= sum over splits of partial[split][tap][k][c]
 __global__ void __launch_bounds__(256)
 dw_fold_kernel(const float *__restrict__ partial, float *dw, int k, int c, int taps, int splits, int accumulate) {
@@ -524,6 +690,7 @@ bool igemm_shape(const katsu_cuda_ctx *ctx, const Shape &g) {
 // Split of the dW contraction over pixel groups and the scratch it needs.
 struct DwPlan {
     size_t bnt, splits, groups_per_split, partial_floats, scratch_floats;
+    bool all_taps;  // narrow layer: conv_dw_taps_kernel, `splits` counts its chunks
 };
 
 DwPlan dw_plan(const katsu_cuda_ctx *ctx, const Shape &g) {
@@ -532,6 +699,16 @@ DwPlan dw_plan(const katsu_cuda_ctx *ctx, const Shape &g) {
     const size_t total_groups = g.n * katsu_div_up(g.ow, 8) * katsu_div_up(g.oh, 4);
     // channel-tile width of the c side: narrow layers get narrow MMAs and operand tiles
     plan.bnt = g.c <= 32 ? 32 : g.c <= 64 ? 64 : 128;
+    const bool three = ctx->precision == KATSU_MODE_3XTF32;
+    // two stages of (g hi/lo 32 KiB + x hi/lo 8 KiB per tap) must fit in shared memory: taps <= 10
+    plan.all_taps = g.c <= 32 && g.k <= (size_t)BM && taps <= 10 && total_groups <= 0x7fffffffu;
+    if (plan.all_taps) {
+        plan.splits = katsu_div_up(total_groups, (size_t)CHUNK);
+        plan.groups_per_split = CHUNK;
+        plan.partial_floats = plan.splits * taps * g.k * g.c;
+        plan.scratch_floats = (padded(g.n * g.c * g.h * g.w) + padded(g.n * g.k * g.oh * g.ow)) * (three ? 2 : 1) + padded(plan.partial_floats);
+        return plan;
+    }
     const size_t out_tiles = katsu_div_up(g.k, (size_t)BM) * katsu_div_up(g.c, plan.bnt) * taps;
     // Split the pixel range so that the grid fills whole waves of the GPU: the smallest split
     // count (at least two blocks' worth of work per SM) whose last wave is >= 95 % full.
@@ -545,7 +722,6 @@ DwPlan dw_plan(const katsu_cuda_ctx *ctx, const Shape &g) {
     plan.groups_per_split = katsu_div_up(total_groups, splits);
     plan.splits = katsu_div_up(total_groups, plan.groups_per_split);
     plan.partial_floats = plan.splits * taps * g.k * g.c;
-    const bool three = ctx->precision == KATSU_MODE_3XTF32;
     plan.scratch_floats = (padded(g.n * g.c * g.h * g.w) + padded(g.n * g.k * g.oh * g.ow)) * (three ? 2 : 1) + padded(plan.partial_floats);
     return plan;
 }
@@ -747,10 +923,28 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr
               nhwc_map(&mx, xt, n, h, wd, c, 8, 4, (int)stride, sw) &&
               nhwc_map(&mx_lo, three ? xt_lo : xt, n, h, wd, c, 8, 4, (int)stride, sw);
     if (!ok) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv dW)");
-    dim3 grid((unsigned)(katsu_div_up(k, (size_t)BM) * katsu_div_up(c, bnt)), (unsigned)taps, (unsigned)splits);
-    auto kernel = bnt == 32 ? conv_dw_igemm_kernel<32> : bnt == 64 ? conv_dw_igemm_kernel<64> : conv_dw_igemm_kernel<128>;
-    KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-    KATSU_LAUNCH(ctx, kernel, grid, 192, kSmemBytes, mg, mg_lo, mx, mx_lo, p);
+    if (plan.all_taps) {
+        DwTapsParams q;
+        q.partial = p.partial;
+        q.n_img = (int)n; q.k = (int)k; q.c = (int)c; q.taps = (int)taps;
+        q.groups_x = p.groups_x; q.groups_y = p.groups_y;
+        q.total_groups = (long long)(n * p.groups_x * p.groups_y);
+        q.chunks = (int)splits;
+        q.stride = (int)stride;
+        q.three_pass = three ? 1 : 0;
+        q.a_groups = (int)katsu_div_up(k, (size_t)32);
+        q.status = ctx->status;
+        for (size_t t = 0; t < taps; ++t) { q.off_y[t] = p.off_y[t]; q.off_x[t] = p.off_x[t]; }
+        const size_t smem = size_t(TAPS_STAGES) * (2 * TILE_BYTES + 2 * taps * 4096) + 1024;
+        KATSU_CUDA_TRY(cudaFuncSetAttribute(conv_dw_taps_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        size_t grid = splits < (size_t)ctx->num_sms ? splits : (size_t)ctx->num_sms;
+        KATSU_LAUNCH(ctx, conv_dw_taps_kernel, (unsigned)grid, 192, smem, mg, mg_lo, mx, mx_lo, q);
+    } else {
+        dim3 grid((unsigned)(katsu_div_up(k, (size_t)BM) * katsu_div_up(c, bnt)), (unsigned)taps, (unsigned)splits);
+        auto kernel = bnt == 32 ? conv_dw_igemm_kernel<32> : bnt == 64 ? conv_dw_igemm_kernel<64> : conv_dw_igemm_kernel<128>;
+        KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        KATSU_LAUNCH(ctx, kernel, grid, 192, kSmemBytes, mg, mg_lo, mx, mx_lo, p);
+    }
     KATSU_LAUNCH(ctx, dw_fold_kernel, (unsigned)katsu_div_up(k * c * taps, (size_t)256), 256, 0, p.partial, dw, (int)k,
                  (int)c, (int)taps, (int)splits, accumulate);
     return KATSU_OK;

@@ -62,3 +62,29 @@ def test_sum(ctx, oracle, count):
         # the reference folds left to right in f32; the device tree sum must be at least as close to exact
         ref = float(oracle.lib().ko_sum(oracle._p(a), oracle._sz(count)))
         assert abs(got - exact) <= abs(ref - exact) + 1e-6 * scale
+
+
+def test_wait_event_orders_two_contexts_of_one_device(ctx):
+    """katsu_cuda_wait_event: work queued on a second context after the wait sees what the first
+    context queued before the record, without a host synchronisation in between."""
+    from katsu_b200 import cabi
+
+    other = cabi.Context(0)
+    try:
+        n = 1 << 22
+        a = ctx.upload(np.full(n, 1.5, np.float32))
+        b, c = ctx.alloc(n), ctx.alloc(n)
+        ctx.sync()
+        ev = ctx.event()
+        for _ in range(4):  # a little queue on the first stream
+            ctx.call("katsu_cuda_add", a, a, b, n)
+        ctx.record(ev)
+        other.wait_event(ev)
+        other.call("katsu_cuda_add", b, a, c, n)  # must see b = 3.0 everywhere
+        out = other.download(c, n)
+        assert np.all(out == 4.5)
+        ctx.event_destroy(ev)
+        for p in (a, b, c):
+            ctx.free(p)
+    finally:
+        other.close()
