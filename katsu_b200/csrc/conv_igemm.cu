@@ -606,18 +606,30 @@ conv_dw_taps_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
     if (warp == 5) tmem_dealloc(tmem_base, tmem_cols);
 }
 
-// dw[k][c][tap] (+)= sum over splits of partial[split][tap][k][c]
+// dw[k][c][tap] (+)= sum over splits of partial[split][tap][k][c].  A block handles 32 elements:
+// eight thread groups each add every eighth partial, then one group adds the eight sums -- a fixed
+// order (bit-reproducible) with eight times the loads in flight of a flat loop, which matters when
+// the all-taps kernel leaves a thousand chunks to fold.
 __global__ void __launch_bounds__(256)
 dw_fold_kernel(const float *__restrict__ partial, float *dw, int k, int c, int taps, int splits, int accumulate) {
+    __shared__ float sums[8][32];
     const size_t elems = size_t(k) * c * taps;
-    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= elems) return;
-    const int t = int(i % taps);
-    const int cc = int((i / taps) % c);
-    const int kk = int(i / (size_t(taps) * c));
+    // walk the partials in their own order ([tap][k][c], contiguous loads); dw is [k][c][tap]
+    const size_t j = size_t(blockIdx.x) * 32 + (threadIdx.x & 31);
+    const int part = threadIdx.x >> 5;
     float s = 0.f;
-    for (int q = 0; q < splits; ++q) s += partial[((size_t(q) * taps + t) * k + kk) * c + cc];
-    dw[i] = accumulate ? dw[i] + s : s;
+    if (j < elems)
+        for (int q = part; q < splits; q += 8) s += partial[size_t(q) * elems + j];
+    sums[part][threadIdx.x & 31] = s;
+    __syncthreads();
+    if (part == 0 && j < elems) {
+        float total = sums[0][threadIdx.x];
+#pragma unroll
+        for (int q = 1; q < 8; ++q) total += sums[q][threadIdx.x];
+        const size_t kc = size_t(k) * c;
+        const size_t i = (j % kc) * taps + j / kc;
+        dw[i] = accumulate ? dw[i] + total : total;
+    }
 }
 
 // ---- host side --------------------------------------------------------------------------
@@ -945,7 +957,7 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr
         KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
         KATSU_LAUNCH(ctx, kernel, grid, 192, kSmemBytes, mg, mg_lo, mx, mx_lo, p);
     }
-    KATSU_LAUNCH(ctx, dw_fold_kernel, (unsigned)katsu_div_up(k * c * taps, (size_t)256), 256, 0, p.partial, dw, (int)k,
+    KATSU_LAUNCH(ctx, dw_fold_kernel, (unsigned)katsu_div_up(k * c * taps, (size_t)32), 256, 0, p.partial, dw, (int)k,
                  (int)c, (int)taps, (int)splits, accumulate);
     return KATSU_OK;
 }
