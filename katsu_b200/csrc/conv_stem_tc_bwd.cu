@@ -582,13 +582,25 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
     if (warp == DW_MMA_WARP) tmem_dealloc(tmem_base, 256);
 }
 
+// dw (+)= sum over blocks of partial[block][oc][tap].  32 elements per block; eight thread groups
+// each add every eighth partial, one group then adds the eight sums: a fixed order (bit-
+// reproducible) with eight loads per element in flight instead of one (21 -> a few microseconds,
+// which matters when a GPU's share of the batch makes the whole kernel 100 microseconds).
 __global__ void __launch_bounds__(256)
 stem_dw_fold_kernel(const float *__restrict__ partial, float *dw, int elems, int parts, int accumulate) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= elems) return;
+    __shared__ float sums[8][32];
+    const int i = blockIdx.x * 32 + (threadIdx.x & 31), part = threadIdx.x >> 5;
     float s = 0.f;
-    for (int p = 0; p < parts; ++p) s += partial[size_t(p) * elems + i];
-    dw[i] = accumulate ? dw[i] + s : s;
+    if (i < elems)
+        for (int p = part; p < parts; p += 8) s += partial[size_t(p) * elems + i];
+    sums[part][threadIdx.x & 31] = s;
+    __syncthreads();
+    if (part == 0 && i < elems) {
+        float total = sums[0][threadIdx.x];
+#pragma unroll
+        for (int q = 1; q < 8; ++q) total += sums[q][threadIdx.x];
+        dw[i] = accumulate ? dw[i] + total : total;
+    }
 }
 
 template <int CIN>
@@ -621,7 +633,7 @@ int32_t dw_launch(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw
     float *partial = nullptr;
     KATSU_TRY(katsu_scratch(ctx, grid * elems, &partial));
     KATSU_LAUNCH(ctx, kernel, (unsigned)grid, DW_THREADS, smem, map_g, map_x, partial, d);
-    KATSU_LAUNCH(ctx, stem_dw_fold_kernel, (unsigned)katsu_div_up((size_t)elems, (size_t)256), 256, 0, partial, dw, elems,
+    KATSU_LAUNCH(ctx, stem_dw_fold_kernel, (unsigned)katsu_div_up((size_t)elems, (size_t)32), 256, 0, partial, dw, elems,
                  (int)grid, accumulate);
     return KATSU_OK;
 }
