@@ -324,7 +324,7 @@ def run_ours(args):
     x_pin[:] = x_host
     n_lanes = max(1, args.e2e_lanes)
     lanes = [ctx] + [cabi.Context(local_rank) for _ in range(n_lanes - 1)]
-    n_chunks = max(1, min(args.e2e_chunks, n // 16))
+    n_chunks = max(1, min(args.e2e_chunks, n // 8))
     bounds = [dp.shard(n, i, n_chunks) for i in range(n_chunks)]
     per_img_x, per_img_y = c * h * wd, k * spec.oh * spec.ow
     chunk_max = max(cnt for _, cnt in bounds)
@@ -332,13 +332,18 @@ def run_ours(args):
     for lane_ctx in lanes:
         lane_buf.append({"w": lane_ctx.upload(w_host), "x": lane_ctx.alloc(chunk_max * per_img_x),
                          "y": lane_ctx.alloc(chunk_max * per_img_y), "g": lane_ctx.alloc(chunk_max * per_img_y),
-                         "dx": lane_ctx.alloc(chunk_max * per_img_x), "dw": lane_ctx.alloc(w_count)})
+                         "dx": lane_ctx.alloc(chunk_max * per_img_x),
+                         # two dW partials per lane, alternating by step, so that a lane can start the
+                         # next step while lane 0 is still combining (and all-reducing) this one
+                         "dw": [lane_ctx.alloc(w_count), lane_ctx.alloc(w_count)]})
     lane_done = [lane_ctx.event() for lane_ctx in lanes]
+    combined = [ctx.event(), ctx.event()]  # lane 0 has consumed the partials of parity 0 / 1
 
     def e2e_step(slot):
-        # the other lanes must not overwrite their dW partials before lane 0 has added the previous step's
+        par = slot & 1
+        # a lane must not overwrite a dW partial that lane 0 has not yet added (two steps back)
         for lane_ctx in lanes[1:]:
-            lane_ctx.wait_event(lane_done[0])
+            lane_ctx.wait_event(combined[par])
         for i, (first_img, cnt) in enumerate(bounds):
             lane_ctx, b = lanes[i % n_lanes], lane_buf[i % n_lanes]
             cg = (cnt, c, h, wd, k, r, s, spec.stride, spec.pad)
@@ -346,22 +351,23 @@ def run_ours(args):
             lane_ctx.conv2d_fwd(b["x"], b["w"], b["y"], *cg)
             lane_ctx.call("katsu_cuda_add", b["y"], b["y"], b["g"], cnt * per_img_y)
             lane_ctx.conv2d_bwd(b["x"], b["w"], b["g"], b["dx"], 0, *cg, 0)
-            lane_ctx.conv2d_bwd(b["x"], b["w"], b["g"], 0, b["dw"], *cg, 1 if i >= n_lanes else 0)
+            lane_ctx.conv2d_bwd(b["x"], b["w"], b["g"], 0, b["dw"][par], *cg, 1 if i >= n_lanes else 0)
             lane_ctx.d2h_async(dx_pin[first_img * per_img_x:(first_img + cnt) * per_img_x], b["dx"])
+        total = lane_buf[0]["dw"][par]
         for j in range(1, min(n_lanes, n_chunks)):
             lanes[j].record(lane_done[j])
             ctx.wait_event(lane_done[j])
-            ctx.call("katsu_cuda_axpy_acc", lane_buf[0]["dw"], lane_buf[j]["dw"], w_count)
+            ctx.call("katsu_cuda_axpy_acc", total, lane_buf[j]["dw"][par], w_count)
         if world > 1:
             ctx.record(dw_ready)
             comm_ctx.wait_event(dw_ready)
-            comm_ctx.call("katsu_cuda_allreduce_sum", lane_buf[0]["dw"], w_count)
+            comm_ctx.call("katsu_cuda_allreduce_sum", total, w_count)
             comm_ctx.record(dw_reduced)
             ctx.wait_event(dw_reduced)
-        ctx.d2h_async(dw_pin[slot], lane_buf[0]["dw"])
-        ctx.record(lane_done[0])
+        ctx.d2h_async(dw_pin[slot], total)
+        ctx.record(combined[par])
 
-    ctx.record(lane_done[0])
+    ctx.record(combined[0]), ctx.record(combined[1])
     e2e_step(e2e_steps)
     for lane_ctx in lanes:
         lane_ctx.sync()
@@ -434,7 +440,8 @@ def run_ours(args):
         ctx.free(p)
     for lane_ctx, b in zip(lanes, lane_buf):
         for p in b.values():
-            lane_ctx.free(p)
+            for q in (p if isinstance(p, list) else [p]):
+                lane_ctx.free(q)
     for a in [x_pin, dx_pin] + dw_pin:
         ctx.free_pinned(a)
     for lane_ctx in lanes[1:]:
