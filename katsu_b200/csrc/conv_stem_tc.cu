@@ -12,14 +12,15 @@
 // Forward:  Y[pixel, oc] = sum_tap Xcol[pixel, tap] * W[oc, tap]
 //   A = Xcol, 128 pixels x 32 taps, held in TENSOR MEMORY (lane = pixel, column = tap) and
 //       written there with tcgen05.st by "builder" threads from a halo tile of x that TMA
-//       drops into shared
-//       memory (6 rows x 40 columns per channel, the start column rounded down to a
-//       16-byte boundary; out-of-image cells arrive as zeros == the reference's skipped
-//       padding taps), as hi = trunc_tf32(v) and lo = v - hi; taps 27..31 are zero.
+//       drops into shared memory (6 rows x 40 columns per channel, the start column rounded
+//       down to a 16-byte boundary; out-of-image cells arrive as zeros == the reference's
+//       skipped padding taps), as hi = trunc_tf32(v) and lo = v - hi; taps 27..31 are zero.
 //   B = W, oc x 32 taps, K-major, built once per block (hi and lo).
-//   D = 128 x oc f32 in tensor memory, several accumulators so epilogues overlap later MMAs.  3xTF32: lo*hi + hi*lo + hi*hi per k-step; TF32 mode: hi*hi.
-// Blocks are persistent (one per SM) and walk 4x32-pixel tiles with specialised warps
-// (epilogue, builders, MMA issue, TMA loads of x; see the kernel).
+//   D = 128 x oc f32 in tensor memory, several accumulators so epilogues overlap later MMAs.
+//       3xTF32: lo*hi + hi*lo + hi*hi per k-step; TF32 mode: hi*hi.
+// Blocks are persistent (two per SM up to 64 output channels, else one) and walk 4x32-pixel
+// tiles with specialised warps (epilogue, builders, MMA issue, TMA loads of x; see the kernel).
+// The backward kernels of the same shapes are in conv_stem_tc_bwd.cu.
 // The output tile leaves through a shared-memory transpose and 128-bit global stores.
 // Measured alternatives: 64 scalar 128-byte-per-warp stores per thread keep too few bytes
 // in flight (6.5 B/clk per SM), and one TMA tensor store per tile (32 x 4 x K box, 128-byte
@@ -54,8 +55,6 @@ __device__ __forceinline__ float tf32_hi(float v) { return __uint_as_float(__flo
 __device__ __forceinline__ void store_chunk(unsigned char *tile, int row, int chunk, float4 v) {
     st_shared_v4(tile + row * 128 + ((chunk ^ (row & 7)) << 4), v);
 }
-
-constexpr int A_TILE = 128 * 128;  // bytes: 128 rows x 128 B
 
 // Warp roles of the forward kernel, GROUPS = 1 or 2 (10 or 18 warps):
 //   [0, 4G)      G epilogue groups (alternate tiles; warp % 4 selects the TMEM lane quarter)
