@@ -21,8 +21,8 @@
 //   channel in a fixed order, and the 14 x 28 output tile goes out with one TMA store.
 //   The region overlaps its neighbours by one pixel on each side (recomputed, not exchanged),
 //   so no two blocks ever add into the same dX element and results are bit-reproducible.
-//   Two warps issue MMAs (two M-tiles each): one thread sustains one small-N MMA per ~44
-//   cycles, two reach the tensor pipe's rate (measured).
+//   Two warps issue MMAs (two M-tiles each): the elect.sync thread of one converged warp
+//   sustains one N = 32 MMA per ~22 cycles, two such warps reach the pipe's 16 (measured).
 #include "common.cuh"
 #include <string.h>
 
@@ -336,8 +336,9 @@ int32_t dx_launch(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx
 //       TMA: a shift of one pixel is not a 16-byte step).
 //   D = 128 x 64: rows 0-63 hold hi*hi | hi*lo, rows 64-127 hold lo*hi | (lo*lo, unused).
 //       One MMA per 8 pixels does all of 3xTF32.  Two accumulators alternate K-blocks and are
-//       drained into registers every DW_DRAIN K-blocks, which bounds the length of any
-//       tensor-core accumulation chain (its f32 adds lose a little per step) to 2048 pixels.
+//       drained into running sums (shared memory) every DW_DRAIN K-blocks, which bounds the
+//       length of any tensor-core accumulation chain (its f32 adds lose a little per step) to
+//       2048 pixels.
 //   Each block ends with one partial dW in scratch; a second kernel folds the partials in a
 //   fixed order (bit-reproducible, no atomics).
 struct StemDwDims {
