@@ -118,6 +118,13 @@ int32_t katsu_conv_direct_dw(katsu_cuda_ctx *ctx, const float *x, const float *g
 int32_t katsu_umma_gemm(katsu_cuda_ctx *ctx, const float *a, const float *b, float *c, size_t M, size_t N, size_t K,
                         bool a_mn, bool b_mn, int accumulate, int *handled);
 
+// dW of a wide convolution through the GEMM kernel (umma_gemm.cu); maps and staging by the caller.
+struct CUtensorMap_st;
+int32_t katsu_umma_conv_dw(katsu_cuda_ctx *ctx, const CUtensorMap_st *map_g, const CUtensorMap_st *map_x,
+                           const CUtensorMap_st *map_x_lo, float *partial, size_t k, size_t c, size_t taps,
+                           size_t total_groups, size_t groups_x, size_t groups_per_img, size_t stride,
+                           const short *off_y, const short *off_x, size_t splits, size_t groups_per_split);
+
 // Wide-channel implicit-GEMM convolution on the tensor cores (conv_igemm.cu); *handled = 0
 // when the shape is outside what it takes.
 int32_t katsu_conv_igemm_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,

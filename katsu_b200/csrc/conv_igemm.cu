@@ -931,10 +931,19 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr
 
     CUtensorMap mg, mg_lo, mx, mx_lo;
     const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
-    bool ok = nhwc_map(&mg, gt, n, oh, ow, k, 8, 4, 1, sw) && nhwc_map(&mg_lo, three ? gt_lo : gt, n, oh, ow, k, 8, 4, 1, sw) &&
+    // wide layers: the GEMM kernel's convolution mode (g goes through tensor memory, its tiles
+    // are read by builder threads and arrive as dense boxes; its lo halves are not needed)
+    const bool via_gemm = !plan.all_taps && bnt == 128;
+    bool ok = nhwc_map(&mg, gt, n, oh, ow, k, 8, 4, 1, via_gemm ? CU_TENSOR_MAP_SWIZZLE_NONE : sw) &&
+              nhwc_map(&mg_lo, three ? gt_lo : gt, n, oh, ow, k, 8, 4, 1, sw) &&
               nhwc_map(&mx, xt, n, h, wd, c, 8, 4, (int)stride, sw) &&
               nhwc_map(&mx_lo, three ? xt_lo : xt, n, h, wd, c, 8, 4, (int)stride, sw);
     if (!ok) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv dW)");
+    if (via_gemm) {
+        KATSU_TRY(katsu_umma_conv_dw(ctx, &mg, &mx, &mx_lo, p.partial, k, c, taps, n * p.groups_x * p.groups_y,
+                                     (size_t)p.groups_x, size_t(p.groups_x) * p.groups_y, stride, p.off_y, p.off_x,
+                                     splits, (size_t)p.groups_per_split));
+    } else
     if (plan.all_taps) {
         DwTapsParams q;
         q.partial = p.partial;

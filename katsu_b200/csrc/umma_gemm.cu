@@ -50,6 +50,12 @@ struct GemmParams {
     int accumulate;    // only used when splits == 1
     int three_pass;    // 3xTF32
     int *status;
+    // conv_dw = 1: the dW contraction of a convolution.  A = g and B = x are channels-innermost
+    // staging arrays [N][H][W][C] (both MN-major), a k-block is one 8 x 4 group of output pixels,
+    // blockIdx.z = split * taps + tap selects the filter tap whose shifted x window is B, and
+    // every block writes a slab (M = output channels, N = input channels).
+    int conv_dw, taps, groups_x, groups_per_img, stride;
+    short off_y[49], off_x[49];
 };
 
 __global__ void __launch_bounds__(256) split_lo_kernel(const float *__restrict__ x, float *__restrict__ lo, size_t count) {
@@ -66,11 +72,9 @@ constexpr uint32_t A_COL0 = 2 * BN;  // TMEM: [2 accumulators x 128][TS A stages
 // Warps 0-3: drains and the epilogue (TMEM lane quarter = warp).  Warps 4-7: A builders
 // (quarter = warp & 3).  Warp 8: TMA loads of A.  Warp 9: MMA issue.  Warp 10: TMA loads of B.
 // A and B have separate rings because their slots live differently long: an A slot is free once
-// the builders have read it, a B slot only when the MMAs that read it have completed, and a
-// completion becomes visible ~300 cycles after issue with the refill another ~1000 behind.  With
-// one ring of four 48 KiB stages that round trip (~3000 cycles per slot) capped the pipe at 67 %.  (A second builder group and eight
-// drain warps were measured slower: 183 against 193 TFLOP/s at 8192^3; the kernel is bound by
-// L2 -> shared-memory traffic of its 128 x 128 tiles, not by the builders.)
+// the builders have read it, a B slot only when the MMAs that read it have completed.
+// (A second builder group with eight drain warps was measured slower, 183 against 193 TFLOP/s at
+// 8192^3: the builders are not what bounds the kernel.)
 constexpr int RASTER_W = 16;
 constexpr int GEMM_THREADS = 11 * 32, TMA_A_WARP = 8, MMA_WARP = 9, TMA_B_WARP = 10;
 
@@ -96,7 +100,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     const int m0 = tile_m * BM, n0 = tile_n * BN;
     const int kb_total = (p.K + BK - 1) / BK;
-    const int kb_begin = blockIdx.z * p.kblocks_per_split;
+    const int tap = p.conv_dw ? int(blockIdx.z) % p.taps : 0;
+    const int kb_begin = (p.conv_dw ? int(blockIdx.z) / p.taps : int(blockIdx.z)) * p.kblocks_per_split;
     int kb_end = kb_begin + p.kblocks_per_split;
     if (kb_end > kb_total) kb_end = kb_total;
     const int kblocks = kb_end > kb_begin ? kb_end - kb_begin : 0;
@@ -137,7 +142,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             mbar_arrive_expect_tx(&a_full[sa], TILE_BYTES);
             unsigned char *ad = a_slots + sa * TILE_BYTES;
             const int k0 = (kb_begin + i) * BK;
-            if (!A_MN) {
+            if (A_MN && p.conv_dw) {
+                const int gidx = kb_begin + i, img = gidx / p.groups_per_img, r = gidx % p.groups_per_img;
+                for (int j = 0; j < BM / 32; ++j)
+                    tma_load_4d(ad + j * 4096, &map_a, &a_full[sa], m0 + 32 * j, (r % p.groups_x) * 8, (r / p.groups_x) * 4, img);
+            } else if (!A_MN) {
                 tma_load_2d(ad, &map_a, &a_full[sa], k0, m0);
             } else {
                 for (int j = 0; j < BM / 32; ++j) tma_load_2d(ad + j * 4096, &map_a, &a_full[sa], m0 + 32 * j, k0);
@@ -153,7 +162,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const int k0 = (kb_begin + i) * BK;
             for (int part = 0; part < (p.three_pass ? 2 : 1); ++part) {
                 const CUtensorMap *mb = part ? &map_b_lo : &map_b;
-                if (!B_MN) {
+                if (B_MN && p.conv_dw) {
+                    const int gidx = kb_begin + i, img = gidx / p.groups_per_img, r = gidx % p.groups_per_img;
+                    const int x0 = (r % p.groups_x) * 8 * p.stride + p.off_x[tap], y0 = (r / p.groups_x) * 4 * p.stride + p.off_y[tap];
+                    for (int j = 0; j < BN / 32; ++j)
+                        tma_load_4d(bd + part * TILE_BYTES + j * 4096, mb, &b_full[sb], n0 + 32 * j, x0, y0, img);
+                } else if (!B_MN) {
                     tma_load_2d(bd + part * TILE_BYTES, mb, &b_full[sb], k0, n0);
                 } else {
                     for (int j = 0; j < BN / 32; ++j) tma_load_2d(bd + part * TILE_BYTES + j * 4096, mb, &b_full[sb], n0 + 32 * j, k0);
@@ -264,8 +278,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         const int row = m0 + warp * 32 + lane;
         if (alive && row < p.M) {
-            float *out = p.c + (p.splits > 1 ? size_t(blockIdx.z) * p.M * p.N : 0);
-            const bool acc_out = p.accumulate && p.splits == 1;
+            const bool slabs = p.splits > 1 || p.conv_dw;
+            float *out = p.c + (slabs ? size_t(blockIdx.z) * p.M * p.N : 0);
+            const bool acc_out = p.accumulate && !slabs;
 #pragma unroll
             for (int q = 0; q < BN / 32; ++q) {
                 const int c0 = q * 32;
@@ -367,6 +382,7 @@ int32_t launch(katsu_cuda_ctx *ctx, const float *a, const float *b, float *c, si
     p.accumulate = accumulate;
     p.three_pass = three_pass ? 1 : 0;
     p.status = ctx->status;
+    p.conv_dw = 0;
     const size_t smem = size_t(AS + 2 * BS) * TILE_BYTES + 1024;
     auto kernel = umma_gemm_kernel<A_MN, B_MN>;
     KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -399,6 +415,35 @@ extern "C" int32_t katsu_cuda_selftest_wait_timeout(katsu_cuda_ctx *ctx, uint64_
     KATSU_TRY(katsu_bind(ctx));
     KATSU_REQUIRE(cycles >= 1000 && cycles <= 200000000ull, "cycle budget must be between 1e3 and 2e8");
     KATSU_LAUNCH(ctx, wait_timeout_probe_kernel, 1, 32, 0, ctx->status, (long long)cycles);
+    return KATSU_OK;
+}
+
+// dW of a wide convolution through the same kernel (see GemmParams::conv_dw).  The caller has
+// staged g and x (and x's lo halves) channels-innermost and built their tensor maps: g with
+// dense 32-channel x 8 x 4 boxes (read by the builders), x with the 32-byte-atom swizzle (read
+// by the tensor core), stepping `stride` pixels.  partial receives [splits][taps][k][c].
+int32_t katsu_umma_conv_dw(katsu_cuda_ctx *ctx, const CUtensorMap *map_g, const CUtensorMap *map_x,
+                           const CUtensorMap *map_x_lo, float *partial, size_t k, size_t c, size_t taps,
+                           size_t total_groups, size_t groups_x, size_t groups_per_img, size_t stride,
+                           const short *off_y, const short *off_x, size_t splits, size_t groups_per_split) {
+    if (taps > 49 || total_groups > 0x3ffffffu || splits * taps > 65535)
+        return katsu_set_error(KATSU_ERR_UNSUPPORTED, "convolution too large for the dW contraction");
+    GemmParams p;
+    p.c = partial;
+    p.M = (int)k; p.N = (int)c; p.K = (int)(total_groups * BK);
+    p.kblocks_per_split = (int)groups_per_split;
+    p.splits = (int)splits;
+    p.accumulate = 0;
+    p.three_pass = ctx->precision == KATSU_MODE_3XTF32 ? 1 : 0;
+    p.status = ctx->status;
+    p.conv_dw = 1;
+    p.taps = (int)taps; p.groups_x = (int)groups_x; p.groups_per_img = (int)groups_per_img; p.stride = (int)stride;
+    for (size_t t = 0; t < taps; ++t) { p.off_y[t] = off_y[t]; p.off_x[t] = off_x[t]; }
+    const size_t smem = size_t(AS + 2 * BS) * TILE_BYTES + 1024;
+    auto kernel = umma_gemm_kernel<true, true>;
+    KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)(katsu_div_up(c, (size_t)BN) * katsu_div_up(k, (size_t)BM)), 1, (unsigned)(splits * taps));
+    KATSU_LAUNCH(ctx, kernel, grid, GEMM_THREADS, smem, *map_g, *map_x, *map_x_lo, p);
     return KATSU_OK;
 }
 
