@@ -35,28 +35,38 @@ constexpr int MAX_TAPS = 49;
 __device__ __forceinline__ float lo_part(float v) { return v - __uint_as_float(__float_as_uint(v) & 0xFFFFE000u); }
 
 // ---- staging passes ---------------------------------------------------------------
-// [N][C][HW] -> [N][HW][C] through a 32x33 shared tile; optionally also the lo halves.
+// [N][C][HW] -> [N][HW][C] through 32x33 shared tiles; optionally also the lo halves.  A block
+// moves four 32-pixel x 32-channel tiles and issues all of its loads before the first store, so
+// that enough bytes are in flight per SM (one tile per block ran at 3.8 TB/s of traffic).
+constexpr int NHWC_TILES = 4;
+
 __global__ void __launch_bounds__(256)
 nchw_to_nhwc_kernel(const float *__restrict__ src, float *__restrict__ dst, float *__restrict__ dst_lo, int c, int hw) {
-    __shared__ float tile[32][33];
+    __shared__ float tile[NHWC_TILES][32][33];
     const int n = blockIdx.z;
-    const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    const int p0 = blockIdx.x * (32 * NHWC_TILES), c0 = blockIdx.y * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
     const float *s = src + size_t(n) * c * hw;
-    for (int i = ty; i < 32; i += 8) {
-        const int cc = c0 + i, pp = p0 + tx;
-        tile[i][tx] = (cc < c && pp < hw) ? __ldg(s + size_t(cc) * hw + pp) : 0.f;
-    }
-    __syncthreads();
-    for (int i = ty; i < 32; i += 8) {
-        const int pp = p0 + i, cc = c0 + tx;
-        if (pp < hw && cc < c) {
-            const float v = tile[tx][i];
-            const size_t o = (size_t(n) * hw + pp) * c + cc;
-            dst[o] = v;
-            if (dst_lo != nullptr) dst_lo[o] = lo_part(v);
+#pragma unroll
+    for (int t = 0; t < NHWC_TILES; ++t)
+#pragma unroll
+        for (int i = ty; i < 32; i += 8) {
+            const int cc = c0 + i, pp = p0 + 32 * t + tx;
+            tile[t][i][tx] = (cc < c && pp < hw) ? __ldg(s + size_t(cc) * hw + pp) : 0.f;
         }
-    }
+    __syncthreads();
+#pragma unroll
+    for (int t = 0; t < NHWC_TILES; ++t)
+#pragma unroll
+        for (int i = ty; i < 32; i += 8) {
+            const int pp = p0 + 32 * t + i, cc = c0 + tx;
+            if (pp < hw && cc < c) {
+                const float v = tile[t][tx][i];
+                const size_t o = (size_t(n) * hw + pp) * c + cc;
+                dst[o] = v;
+                if (dst_lo != nullptr) dst_lo[o] = lo_part(v);
+            }
+        }
 }
 
 // w[K][C][taps] -> wf[tap][K][C] (forward B, rows = oc) and/or wb[tap][C][K] (dX B, rows = c), with lo halves.
@@ -673,7 +683,7 @@ bool taps_map(CUtensorMap *map, const float *base, size_t taps, size_t rows, siz
 }
 
 int32_t stage_nhwc(katsu_cuda_ctx *ctx, const float *src, float *dst, float *dst_lo, size_t n, size_t c, size_t hw) {
-    dim3 grid((unsigned)katsu_div_up(hw, 32), (unsigned)katsu_div_up(c, 32), (unsigned)n);
+    dim3 grid((unsigned)katsu_div_up(hw, (size_t)32 * NHWC_TILES), (unsigned)katsu_div_up(c, 32), (unsigned)n);
     KATSU_LAUNCH(ctx, nchw_to_nhwc_kernel, grid, 256, 0, src, dst, dst_lo, (int)c, (int)hw);
     return KATSU_OK;
 }
