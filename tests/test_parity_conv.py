@@ -22,6 +22,9 @@ SHAPES = [
     (1, 32, 20, 20, 64, 3, 3, 1, 1), (2, 64, 15, 17, 40, 3, 3, 2, 1), (1, 20, 9, 9, 36, 5, 5, 1, 2),
     (1, 16, 8, 8, 16, 1, 1, 1, 0), (1, 16, 9, 9, 16, 1, 1, 3, 0), (2, 36, 10, 10, 132, 3, 3, 1, 1),
     (1, 16, 10, 12, 16, 2, 3, 1, 1), (3, 160, 7, 9, 144, 3, 3, 1, 1), (1, 24, 33, 32, 20, 3, 3, 2, 1),
+    # narrow layers with more than 64 output channels (three and four 32-channel groups of g in the
+    # all-taps dW kernel), and a wide layer whose channel counts fill only part of a 128-wide tile
+    (1, 32, 12, 12, 100, 3, 3, 1, 1), (2, 20, 9, 11, 128, 3, 3, 2, 1), (1, 96, 10, 10, 80, 3, 3, 2, 1),
     # stencil path: C in 1..4, 3x3, stride 1, pad 1
     (1, 3, 8, 8, 8, 3, 3, 1, 1), (2, 3, 33, 37, 5, 3, 3, 1, 1), (1, 1, 40, 64, 70, 3, 3, 1, 1),
     (2, 4, 9, 36, 9, 3, 3, 1, 1), (3, 2, 17, 5, 64, 3, 3, 1, 1), (2, 3, 64, 64, 32, 3, 3, 1, 1),
