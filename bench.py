@@ -591,8 +591,8 @@ def main():
     ap.add_argument("--scaling", choices=["strong", "weak"], default="strong")
     ap.add_argument("--cpu-sample", type=int, default=32, help="images in the single-thread CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--e2e-chunks", type=int, default=16, help="batch chunks of the end-to-end leg (at least 16 images each)")
-    ap.add_argument("--e2e-lanes", type=int, default=4, help="contexts (streams) the chunks rotate over")
+    ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks of the end-to-end leg (at least 8 images each)")
+    ap.add_argument("--e2e-lanes", type=int, default=8, help="contexts (streams) the chunks rotate over")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (small profiling cases)")
     args = ap.parse_args()
     if args.workload == "small_cnn":
