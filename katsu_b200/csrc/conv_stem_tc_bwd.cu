@@ -385,9 +385,12 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
 
     if (tid == 0) {
         for (int s = 0; s < DW_GS; ++s) { mbar_init(&g_full[s], 1); mbar_init(&g_empty[s], 4); }
-        // one barrier pair per stage for A and B together (4 A-builder warps + 3 B-builder warps
-        // fill it, one commit frees it): every wait in the MMA warp's loop costs ~90 cycles
-        for (int s = 0; s < DW_AS; ++s) { mbar_init(&ab_full[s], 7); mbar_init(&ab_empty[s], 1); }
+        // one barrier pair per stage for A and B together (4 A-builder warps + 96 B-builder
+        // threads fill it, one commit frees it): every wait in the MMA warp's loop costs ~90 cycles.
+        // The B tile is written with ordinary stores and read by the tensor core (async proxy), so
+        // every writing thread fences and arrives itself; the A stage is written with tcgen05.st,
+        // whose completion each thread has waited for, so one arrival per warp is enough there.
+        for (int s = 0; s < DW_AS; ++s) { mbar_init(&ab_full[s], 4 + 96); mbar_init(&ab_empty[s], 1); }
         for (int s = 0; s < DW_XS; ++s) { mbar_init(&x_full[s], 1); mbar_init(&x_empty[s], 3); }
         mbar_init(&d_full, 1);
         mbar_init(&d_empty, 4);
@@ -522,7 +525,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
                     }
                 }
                 fence_proxy_async_smem();
-                mbar_arrive_warp(&ab_full[bs]);
+                mbar_arrive(&ab_full[bs]);
                 PROF_MARK(3)
             }
             if (!ok) break;
