@@ -223,7 +223,9 @@ def run_ours(args):
     spec = spec_full.with_batch(images)
     x_host, w_host = workloads.conv_inputs(spec_full, first, images)
 
+    precision = {"3xtf32": 0, "tf32": 1, "fp32": 2}[args.precision]
     ctx = cabi.Context(local_rank)
+    ctx.set_precision(precision)
     # The dW all-reduce runs on a second context (stream) of the device so that it overlaps the dX
     # kernel, which does not depend on it; events order the two streams, the host never blocks.
     comm_ctx = None
@@ -318,12 +320,14 @@ def run_ours(args):
     # the host synchronises once after the last step, so consecutive steps pipeline as well.
     for p in (py, pg, pdx):
         ctx.free(p)
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = args.e2e_steps or max(3, min(args.steps, 10))
     x_pin, dx_pin = ctx.pinned(x_count), ctx.pinned(x_count)
     dw_pin = [ctx.pinned(w_count) for _ in range(e2e_steps + 1)]
     x_pin[:] = x_host
     n_lanes = max(1, args.e2e_lanes)
     lanes = [ctx] + [cabi.Context(local_rank) for _ in range(n_lanes - 1)]
+    for lane_ctx in lanes[1:]:
+        lane_ctx.set_precision(precision)
     n_chunks = max(1, min(args.e2e_chunks, n // 8))
     bounds = [dp.shard(n, i, n_chunks) for i in range(n_chunks)]
     per_img_x, per_img_y = c * h * wd, k * spec.oh * spec.ow
@@ -433,7 +437,8 @@ def run_ours(args):
             "e2e": {"value": global_batch / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 4 * x_count, "d2h_bytes_per_step": 4 * (x_count + w_count),
                     "pipeline": f"{n_chunks} batch chunks over {n_lanes} streams, pinned host buffers, one host sync after the last step",
-                    "dw_step_spread": dw_spread},
+                    "dw_step_spread": dw_spread,
+                    "dw_steps_differing": sum(1 for i in range(1, e2e_steps) if not np.array_equal(dw_pin[0], dw_pin[i]))},
             "gpu_launches": launches,
             "clocks": clocks.summary(),
         }
@@ -596,6 +601,9 @@ def main():
     ap.add_argument("--scaling", choices=["strong", "weak"], default="strong")
     ap.add_argument("--cpu-sample", type=int, default=32, help="images in the single-thread CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--precision", choices=["3xtf32", "tf32", "fp32"], default="3xtf32",
+                    help="contraction mode of the kernels (the metric is quoted on the default)")
+    ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the end-to-end leg (default: min(steps, 10))")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks of the end-to-end leg (at least 8 images each)")
     ap.add_argument("--e2e-lanes", type=int, default=8, help="contexts (streams) the chunks rotate over")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (small profiling cases)")

@@ -26,6 +26,9 @@ struct katsu_cuda_ctx {
     // set by conv2d_bwd while one call computes both dX and dW on the implicit-GEMM path: the dX
     // launch stages g (channels-innermost copy) where the dW launch expects it, once for both
     int share_g_staging, g_staged;
+    // diagnostic: which low-channel tensor-core kernels may be used (bit 0 forward, 1 dX, 2 dW);
+    // from the environment variable KATSU_STEM_TC_MASK at context creation, default all
+    int stem_tc_mask;
     // Buffer written by katsu_cuda_flush_l2.
     float *flush;
     size_t flush_floats;

@@ -5,6 +5,7 @@
 #include <new>
 
 #include "common.cuh"
+#include <stdlib.h>
 
 static thread_local char g_error[512] = "";
 
@@ -73,6 +74,8 @@ extern "C" int32_t katsu_cuda_init(int32_t device, katsu_cuda_ctx **out_ctx) {
     ctx->device = device;
     ctx->num_sms = prop.multiProcessorCount;
     ctx->precision = KATSU_MODE_3XTF32;
+    ctx->stem_tc_mask = 7;
+    if (const char *mask = getenv("KATSU_STEM_TC_MASK")) ctx->stem_tc_mask = atoi(mask) & 7;
     // katsu_cuda_alloc / katsu_cuda_free are stream-ordered (cudaMallocAsync on the device's
     // default pool).  Keep freed blocks cached: an autograd step allocates and frees the same
     // few hundred MB of adjoint buffers every time, and cudaMalloc / cudaFree each cost a

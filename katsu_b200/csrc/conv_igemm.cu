@@ -149,7 +149,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], 4);
+            mbar_init(&acc_empty[b], 128);
         }
         mbar_init_fence();
     }
@@ -264,7 +264,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 if (last_group) {
                     // everything this tile needs from the accumulators is in registers now
                     tc_fence_before_sync();
-                    mbar_arrive_warp(&acc_empty[b]);
+                    mbar_arrive(&acc_empty[b]);
                 }
                 if (pixel_ok) {
 #pragma unroll
@@ -499,7 +499,7 @@ conv_dw_taps_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
             mbar_init(&empty[s], 1);
         }
         mbar_init(&acc_full, 1);
-        mbar_init(&acc_empty, 4);
+        mbar_init(&acc_empty, 128);
         mbar_init_fence();
     }
     if (warp == 5) {
@@ -600,7 +600,7 @@ conv_dw_taps_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
                 tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + uint32_t(t) * 32, v);
                 if (t == p.taps - 1) {
                     tc_fence_before_sync();
-                    mbar_arrive_warp(&acc_empty);
+                    mbar_arrive(&acc_empty);
                 }
                 if (oc < p.k) {
                     float *dst = p.partial + ((size_t(chunk) * p.taps + t) * p.k + oc) * p.c;

@@ -100,12 +100,12 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
 
     if (tid == 0) {
         for (int s = 0; s < 3; ++s) {
-            mbar_init(&full[s], 4);
+            mbar_init(&full[s], 128);
             mbar_init(&empty[s], 1);
         }
         for (int s = 0; s < 4; ++s) {
             mbar_init(&acc_full[s], 1);
-            mbar_init(&acc_empty[s], 4);
+            mbar_init(&acc_empty[s], 128);
         }
         for (int s = 0; s < XS; ++s) {
             mbar_init(&x_full[s], 1);
@@ -175,7 +175,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
             if (d.three_pass) tmem_st_32x32(a_addr + 32, lo);
             tmem_st_wait();
             tc_fence_before_sync();
-            mbar_arrive_warp(&full[s]);
+            mbar_arrive(&full[s]);  // every thread, after its own tcgen05.wait::st
             PROF_MARK(3)
         }
         if (r == 0 && group == 0) PROF_DUMP(0)
@@ -267,7 +267,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
                 }
                 if (alive && c0 + 64 >= d.np) {
                     tc_fence_before_sync();
-                    mbar_arrive_warp(&acc_empty[b]);  // the accumulator is free as soon as it has been read
+                    mbar_arrive(&acc_empty[b]);  // every thread, after its own tcgen05.wait::ld
                 }
                 PROF_MARK(1)
                 named_barrier(bar_id, 128);
@@ -343,6 +343,7 @@ int32_t katsu_conv_stem_tc_fwd(katsu_cuda_ctx *ctx, const float *x, const float 
                                size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
                                size_t stride, size_t pad, int *handled) {
     *handled = 0;
+    if (!(ctx->stem_tc_mask & 1)) return KATSU_OK;
     if (!stem_tc_shape(ctx, n, c, h, wd, k, r, s, stride, pad)) return KATSU_OK;
     if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0 || (reinterpret_cast<uintptr_t>(y) & 15u) != 0) return KATSU_OK;
     *handled = 1;

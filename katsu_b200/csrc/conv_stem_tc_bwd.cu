@@ -92,10 +92,10 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
             mbar_init(&g_empty[s], 8);
         }
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&a_full[s], 8);
+            mbar_init(&a_full[s], 256);
             mbar_init(&a_empty[s], 2);
             mbar_init(&d_full[s], 2);
-            mbar_init(&d_empty[s], 4);
+            mbar_init(&d_empty[s], 128);
         }
         mbar_init_fence();
     }
@@ -157,7 +157,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
                 tmem_st_32x32(a_addr + 32, v[1]);
                 tmem_st_wait();
                 tc_fence_before_sync();
-                mbar_arrive_warp(&a_full[as]);
+                mbar_arrive(&a_full[as]);
                 PROF_MARK(3)
             }
             if (!ok) break;
@@ -256,7 +256,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
                     for (int t = 0; t < TAPS; ++t) st_shared_f32(zp + t * DX_ZP, v[t]);
                 }
                 tc_fence_before_sync();
-                mbar_arrive_warp(&d_empty[db]);
+                mbar_arrive(&d_empty[db]);
             }
             if (tid == 0) tma_store_wait_read<0>();  // the previous tile's store has read `outs`
             named_barrier(1, 128);
@@ -385,15 +385,13 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
 
     if (tid == 0) {
         for (int s = 0; s < DW_GS; ++s) { mbar_init(&g_full[s], 1); mbar_init(&g_empty[s], 4); }
-        // one barrier pair per stage for A and B together (4 A-builder warps + 96 B-builder
+        // one barrier pair per stage for A and B together (128 A-builder threads + 96 B-builder
         // threads fill it, one commit frees it): every wait in the MMA warp's loop costs ~90 cycles.
-        // The B tile is written with ordinary stores and read by the tensor core (async proxy), so
-        // every writing thread fences and arrives itself; the A stage is written with tcgen05.st,
-        // whose completion each thread has waited for, so one arrival per warp is enough there.
-        for (int s = 0; s < DW_AS; ++s) { mbar_init(&ab_full[s], 4 + 96); mbar_init(&ab_empty[s], 1); }
+        // Every thread arrives itself, after its own tcgen05.wait::st (A) or proxy fence (B).
+        for (int s = 0; s < DW_AS; ++s) { mbar_init(&ab_full[s], 128 + 96); mbar_init(&ab_empty[s], 1); }
         for (int s = 0; s < DW_XS; ++s) { mbar_init(&x_full[s], 1); mbar_init(&x_empty[s], 3); }
         mbar_init(&d_full, 1);
-        mbar_init(&d_empty, 4);
+        mbar_init(&d_empty, 128);
         mbar_init_fence();
     }
     if (warp == DW_MMA_WARP) {
@@ -430,7 +428,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
                 }
             }
             tc_fence_before_sync();
-            mbar_arrive_warp(&d_empty);
+            mbar_arrive(&d_empty);
             return true;
         };
         PROF_DECL
@@ -467,7 +465,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
             tmem_st_32x32(lane_addr + DW_A_COL0 + uint32_t(as) * 32, v);
             tmem_st_wait();
             tc_fence_before_sync();
-            mbar_arrive_warp(&ab_full[as]);
+            mbar_arrive(&ab_full[as]);
             PROF_MARK(3)
         }
         if (tid == 0) PROF_DUMP(0)
@@ -647,7 +645,7 @@ int32_t dw_launch(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw
 int32_t katsu_conv_stem_tc_dx(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx, size_t n, size_t c,
                               size_t h, size_t wd, size_t k, int accumulate, int *handled) {
     *handled = 0;
-    if (ctx->precision == KATSU_MODE_FP32) return KATSU_OK;
+    if (ctx->precision == KATSU_MODE_FP32 || !(ctx->stem_tc_mask & 2)) return KATSU_OK;
     if (c < 1 || c > 3 || k < 1 || k > 128 || h > 32768 || wd > 32768 || wd % 4 != 0) return KATSU_OK;
     if ((reinterpret_cast<uintptr_t>(g) & 15u) != 0 || (reinterpret_cast<uintptr_t>(dx) & 15u) != 0) return KATSU_OK;
     StemDxDims d;
@@ -671,7 +669,7 @@ int32_t katsu_conv_stem_tc_dx(katsu_cuda_ctx *ctx, const float *w, const float *
 int32_t katsu_conv_stem_tc_dw(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw, size_t n, size_t c,
                               size_t h, size_t wd, size_t k, int accumulate, int *handled) {
     *handled = 0;
-    if (ctx->precision == KATSU_MODE_FP32) return KATSU_OK;
+    if (ctx->precision == KATSU_MODE_FP32 || !(ctx->stem_tc_mask & 4)) return KATSU_OK;
     if (c < 1 || c > 3 || k < 1 || k > 64 || n == 0 || h > 32768 || wd > 32768 || wd % 4 != 0) return KATSU_OK;
     if ((reinterpret_cast<uintptr_t>(g) & 15u) != 0 || (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return KATSU_OK;
     StemDwDims d;

@@ -118,10 +118,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         for (int s = 0; s < TS; ++s) {
             mbar_init(&t_free[s], 1);
-            mbar_init(&a_ready[s], 4);
+            mbar_init(&a_ready[s], 128);
         }
         mbar_init(&batch_done, 1);
-        mbar_init(&drained, 4);
+        mbar_init(&drained, 128);
         mbar_init_fence();
     }
     if (warp == MMA_WARP) {
@@ -206,7 +206,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
             tmem_st_wait();
             tc_fence_before_sync();
-            mbar_arrive_warp(&a_ready[s]);
+            mbar_arrive(&a_ready[s]);
         }
     } else if (warp == MMA_WARP) {
         // ---- MMA issue: the whole warp runs the loop, the thread chosen by elect.sync issues ----
@@ -273,7 +273,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     }
                 }
                 tc_fence_before_sync();
-                mbar_arrive_warp(&drained);
+                mbar_arrive(&drained);
             }
         }
         const int row = m0 + warp * 32 + lane;
