@@ -145,7 +145,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
         PROF_DECL
         for (int it = group; it < my_tiles; it += GROUPS) {
             const int s = it % AS, xs = it % XS;
-            if (!mbar_wait_warp(&x_full[xs], (it / XS) & 1, d.status, 45)) break;
+            if (!mbar_wait_warp_ready(&x_full[xs], (it / XS) & 1, d.status, 45)) break;
             PROF_MARK(0)
             float v[32];
             const float *xt = x_tiles[xs] + win;
@@ -160,7 +160,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
             __syncwarp();
             if (lane == 0) mbar_arrive(&x_empty[xs]);  // this warp has read its part of the x tile
             PROF_MARK(1)
-            if (it >= AS && !mbar_wait_warp(&empty[s], ((it / AS) - 1) & 1, d.status, 41)) break;
+            if (it >= AS && !mbar_wait_warp_ready(&empty[s], ((it / AS) - 1) & 1, d.status, 41)) break;
             tc_fence_after_sync();
             PROF_MARK(2)
             const uint32_t a_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + a_col0 + uint32_t(s) * 64;
@@ -205,9 +205,9 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
         PROF_DECL
         for (int it = 0; it < my_tiles; ++it) {
             const int s = it % AS, b = it % NB;
-            if (!mbar_wait_warp(&full[s], (it / AS) & 1, d.status, 42)) break;
+            if (!mbar_wait_warp_ready(&full[s], (it / AS) & 1, d.status, 42)) break;
             PROF_MARK(0)
-            if (it >= NB && !mbar_wait_warp(&acc_empty[b], ((it / NB) - 1) & 1, d.status, 43)) break;
+            if (it >= NB && !mbar_wait_warp_ready(&acc_empty[b], ((it / NB) - 1) & 1, d.status, 43)) break;
             PROF_MARK(1)
             tc_fence_after_sync();
             const uint32_t acc = tmem_base + uint32_t(b) * d.np;
@@ -248,7 +248,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
             // A warp whose wait ran out keeps meeting its group at the named barriers (the others
             // may have got through just before) and skips the work; once one wait of the launch
             // has failed all later waits return at once, so the rest of the loop is quick.
-            if (alive) alive = mbar_wait_warp(&acc_full[b], (it / NB) & 1, d.status, 44);
+            if (alive) alive = mbar_wait_warp_ready(&acc_full[b], (it / NB) & 1, d.status, 44);
             tc_fence_after_sync();
             PROF_MARK(0)
             const int tile = blockIdx.x + it * gridDim.x;
