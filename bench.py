@@ -325,9 +325,19 @@ def run_ours(args):
     dw_pin = [ctx.pinned(w_count) for _ in range(e2e_steps + 1)]
     x_pin[:] = x_host
     n_lanes = max(1, args.e2e_lanes)
-    lanes = [ctx] + [cabi.Context(local_rank) for _ in range(n_lanes - 1)]
-    for lane_ctx in lanes[1:]:
+    # The tcgen05 forward kernel has produced wrong tiles when other streams' element-wise kernels ran
+    # beside it (an open defect; single-stream use is unaffected).  The streams of this leg therefore
+    # get contexts whose forward stays on the CUDA-core stencil (KATSU_STEM_TC_MASK is read when a
+    # context is created); dX and dW keep their tensor-core kernels.
+    saved_mask = os.environ.get("KATSU_STEM_TC_MASK")
+    if n_lanes > 1 and saved_mask is None:
+        os.environ["KATSU_STEM_TC_MASK"] = "6"
+    lanes = [cabi.Context(local_rank) for _ in range(n_lanes)]
+    if saved_mask is None:
+        os.environ.pop("KATSU_STEM_TC_MASK", None)
+    for lane_ctx in lanes:
         lane_ctx.set_precision(precision)
+    lead = lanes[0]
     n_chunks = max(1, min(args.e2e_chunks, n // 8))
     bounds = [dp.shard(n, i, n_chunks) for i in range(n_chunks)]
     per_img_x, per_img_y = c * h * wd, k * spec.oh * spec.ow
@@ -341,7 +351,7 @@ def run_ours(args):
                          # next step while lane 0 is still combining (and all-reducing) this one
                          "dw": [lane_ctx.alloc(w_count), lane_ctx.alloc(w_count)]})
     lane_done = [lane_ctx.event() for lane_ctx in lanes]
-    combined = [ctx.event(), ctx.event()]  # lane 0 has consumed the partials of parity 0 / 1
+    combined = [lead.event(), lead.event()]  # lane 0 has consumed the partials of parity 0 / 1
 
     def e2e_step(slot):
         par = slot & 1
@@ -360,18 +370,18 @@ def run_ours(args):
         total = lane_buf[0]["dw"][par]
         for j in range(1, min(n_lanes, n_chunks)):
             lanes[j].record(lane_done[j])
-            ctx.wait_event(lane_done[j])
-            ctx.call("katsu_cuda_axpy_acc", total, lane_buf[j]["dw"][par], w_count)
+            lead.wait_event(lane_done[j])
+            lead.call("katsu_cuda_axpy_acc", total, lane_buf[j]["dw"][par], w_count)
         if world > 1:
-            ctx.record(dw_ready)
+            lead.record(dw_ready)
             comm_ctx.wait_event(dw_ready)
             comm_ctx.call("katsu_cuda_allreduce_sum", total, w_count)
             comm_ctx.record(dw_reduced)
-            ctx.wait_event(dw_reduced)
-        ctx.d2h_async(dw_pin[slot], total)
-        ctx.record(combined[par])
+            lead.wait_event(dw_reduced)
+        lead.d2h_async(dw_pin[slot], total)
+        lead.record(combined[par])
 
-    ctx.record(combined[0]), ctx.record(combined[1])
+    lead.record(combined[0]), lead.record(combined[1])
     e2e_step(e2e_steps)
     for lane_ctx in lanes:
         lane_ctx.sync()
@@ -437,6 +447,7 @@ def run_ours(args):
             "e2e": {"value": global_batch / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 4 * x_count, "d2h_bytes_per_step": 4 * (x_count + w_count),
                     "pipeline": f"{n_chunks} batch chunks over {n_lanes} streams, pinned host buffers, one host sync after the last step",
+                    "forward_kernel": "CUDA-core stencil (multi-stream leg)" if n_lanes > 1 else "tcgen05",
                     "dw_step_spread": dw_spread,
                     "dw_steps_differing": sum(1 for i in range(1, e2e_steps) if not np.array_equal(dw_pin[0], dw_pin[i]))},
             "gpu_launches": launches,
@@ -454,7 +465,7 @@ def run_ours(args):
                 lane_ctx.free(q)
     for a in [x_pin, dx_pin] + dw_pin:
         ctx.free_pinned(a)
-    for lane_ctx in lanes[1:]:
+    for lane_ctx in lanes:
         lane_ctx.close()
     if world > 1:
         comm_ctx.call("katsu_cuda_comm_destroy")
