@@ -157,8 +157,11 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
                 for (int ky = 0; ky < 3; ++ky)
 #pragma unroll
                     for (int kx = 0; kx < 3; ++kx) v[(c * 3 + ky) * 3 + kx] = ld_shared_f32(xt + (c * 6 + ky) * 40 + kx);
+            // Release the x stage: the window values are in registers.  The refill is an async-proxy
+            // (TMA) write after generic-proxy reads, hence the proxy fence before the arrival.
+            fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&x_empty[xs]);  // this warp has read its part of the x tile
+            if (lane == 0) mbar_arrive(&x_empty[xs]);
             PROF_MARK(1)
             if (it >= AS && !mbar_wait_warp_ready(&empty[s], ((it / AS) - 1) & 1, d.status, 41)) break;
             tc_fence_after_sync();

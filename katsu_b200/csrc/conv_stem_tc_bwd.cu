@@ -146,6 +146,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
                         v[m][16 + oc] = val - hi;
                     }
                 }
+                fence_proxy_async_smem();  // ordinary reads of the stage before its TMA refill
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&g_empty[gs]);
                 PROF_MARK(1)
@@ -456,6 +457,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
                     for (int t = 0; t < 32; ++t) v[t] = 0.f;
                 }
             }
+            fence_proxy_async_smem();  // ordinary reads of the stage before its TMA refill
             __syncwarp();
             if (lane == 0) mbar_arrive(&g_empty[gs]);
             PROF_MARK(1)
@@ -527,6 +529,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
                 PROF_MARK(3)
             }
             if (!ok) break;
+            fence_proxy_async_smem();  // ordinary reads of the stage before its TMA refill
             __syncwarp();
             if (lane == 0) mbar_arrive(&x_empty[xs]);
         }

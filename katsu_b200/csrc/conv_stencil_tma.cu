@@ -107,6 +107,7 @@ stencil_dx_tma_kernel(const __grid_constant__ CUtensorMap map_g, const float *__
                             for (int p = 0; p < 4; ++p)
                                 acc[c][q][p] = fmaf(gw[q + 2 - ky][p + 2 - kx], wv[(c * 3 + ky) * 3 + kx], acc[c][q][p]);
         }
+        fence_proxy_async_smem();  // ordinary reads of the stage before its TMA refill
         __syncthreads();  // stage s may be refilled from the next iteration on
     }
     if (!alive) return;
@@ -264,6 +265,7 @@ stencil_dw_tma_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_co
                                 acc1[(c * 3 + ky) * 3 + kx] = fmaf(g1[p], xw[c][ky][p + kx], acc1[(c * 3 + ky) * 3 + kx]);
                             }
             }
+            fence_proxy_async_smem();  // ordinary reads of the stage before its TMA refill
             __syncthreads();  // stage s may be refilled
         }
         if (!alive) return;

@@ -195,6 +195,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
                 for (int k = 0; k < 32; ++k) v[k] = ld_shared_f32(ad + quarter * 4096 + k * 128 + lane * 4);
             }
+            fence_proxy_async_smem();  // ordinary reads of the slot before its TMA refill
             mbar_arrive_warp(&a_read[sa]);
             if (i >= TS && !mbar_wait_warp_ready(&t_free[s], ((i / TS) - 1) & 1, p.status, 15)) break;
             tc_fence_after_sync();
