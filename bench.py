@@ -325,16 +325,9 @@ def run_ours(args):
     dw_pin = [ctx.pinned(w_count) for _ in range(e2e_steps + 1)]
     x_pin[:] = x_host
     n_lanes = max(1, args.e2e_lanes)
-    # The tcgen05 forward kernel has produced wrong tiles when other streams' element-wise kernels ran
-    # beside it (an open defect; single-stream use is unaffected).  The streams of this leg therefore
-    # get contexts whose forward stays on the CUDA-core stencil (KATSU_STEM_TC_MASK is read when a
-    # context is created); dX and dW keep their tensor-core kernels.
-    saved_mask = os.environ.get("KATSU_STEM_TC_MASK")
-    if n_lanes > 1 and saved_mask is None:
-        os.environ["KATSU_STEM_TC_MASK"] = "6"
+    # Each lane is a context of its own (one stream each); all run the same tensor-core kernels as the
+    # device-timed leg.  KATSU_STEM_TC_MASK, when set by the caller, still applies to them.
     lanes = [cabi.Context(local_rank) for _ in range(n_lanes)]
-    if saved_mask is None:
-        os.environ.pop("KATSU_STEM_TC_MASK", None)
     for lane_ctx in lanes:
         lane_ctx.set_precision(precision)
     lead = lanes[0]
@@ -447,7 +440,7 @@ def run_ours(args):
             "e2e": {"value": global_batch / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 4 * x_count, "d2h_bytes_per_step": 4 * (x_count + w_count),
                     "pipeline": f"{n_chunks} batch chunks over {n_lanes} streams, pinned host buffers, one host sync after the last step",
-                    "forward_kernel": "CUDA-core stencil (multi-stream leg)" if n_lanes > 1 else "tcgen05",
+                    "forward_kernel": "tcgen05" if os.environ.get("KATSU_STEM_TC_MASK") is None else "KATSU_STEM_TC_MASK=" + os.environ["KATSU_STEM_TC_MASK"],
                     "dw_step_spread": dw_spread,
                     "dw_steps_differing": sum(1 for i in range(1, e2e_steps) if not np.array_equal(dw_pin[0], dw_pin[i]))},
             "gpu_launches": launches,
