@@ -1,0 +1,89 @@
+"""Several contexts (one stream each) of one device running the low-channel convolution kernels side by side.
+
+Each stream's output must equal, bit for bit, what the same stream produced alone.  The element-wise kernel
+between the convolutions is what puts another stream's memory traffic beside the pipelined kernels; without a
+proxy fence before a TMA-written shared-memory stage is released for its refill, that timing made the forward
+kernel compute whole pixels from the next tile's input window."""
+import numpy as np
+import pytest
+
+from katsu_b200 import cabi, workloads
+
+pytestmark = pytest.mark.gpu
+
+LANES = 4
+REPEATS = 5
+
+
+def _lanes(spec):
+    x, w = workloads.conv_inputs(spec)
+    lanes = []
+    for i in range(LANES):
+        context = cabi.Context(0)
+        xi = (x * np.float32(i + 1)).astype(np.float32)  # distinct inputs per stream
+        lanes.append((context, context.upload(xi), context.upload(w)))
+    return lanes
+
+
+def _close(lanes, extra):
+    for (context, px, pw), pointers in zip(lanes, extra):
+        for p in (px, pw, *pointers):
+            context.free(p)
+        context.close()
+
+
+def test_forward_beside_other_streams_is_bit_identical():
+    spec = workloads.CONV["stem_256x3x224"].with_batch(16)
+    geom = (spec.n, spec.c, spec.h, spec.w, spec.k, spec.r, spec.s, spec.stride, spec.pad)
+    y_count = spec.n * spec.k * spec.oh * spec.ow
+    lanes = _lanes(spec)
+    extra, alone = [], []
+    for context, px, pw in lanes:
+        py, pg = context.alloc(y_count), context.alloc(y_count)
+        context.conv2d_fwd(px, pw, py, *geom)
+        context.sync()
+        alone.append(context.download(py, y_count).copy())
+        extra.append((py, pg))
+    try:
+        for _ in range(REPEATS):
+            for _ in range(3):
+                for (context, px, pw), (py, pg) in zip(lanes, extra):
+                    context.conv2d_fwd(px, pw, py, *geom)
+                    context.call("katsu_cuda_add", py, py, pg, y_count)
+            for context, _, _ in lanes:
+                context.sync()
+            for (context, _, _), (py, _), expect in zip(lanes, extra, alone):
+                assert np.array_equal(context.download(py, y_count), expect)
+    finally:
+        _close(lanes, extra)
+
+
+def test_backward_beside_other_streams_is_bit_identical():
+    spec = workloads.CONV["stem_256x3x224"].with_batch(16)
+    geom = (spec.n, spec.c, spec.h, spec.w, spec.k, spec.r, spec.s, spec.stride, spec.pad)
+    x_count = spec.n * spec.c * spec.h * spec.w
+    w_count = spec.k * spec.c * spec.r * spec.s
+    y_count = spec.n * spec.k * spec.oh * spec.ow
+    rng = np.random.default_rng(7)
+    g = rng.standard_normal(y_count).astype(np.float32)
+    lanes = _lanes(spec)
+    extra, alone = [], []
+    for context, px, pw in lanes:
+        pg, pdx, pdw, ptmp = context.upload(g), context.alloc(x_count), context.alloc(w_count), context.alloc(y_count)
+        context.conv2d_bwd(px, pw, pg, pdx, pdw, *geom)
+        context.sync()
+        alone.append((context.download(pdx, x_count).copy(), context.download(pdw, w_count).copy()))
+        extra.append((pg, pdx, pdw, ptmp))
+    try:
+        for _ in range(REPEATS):
+            for _ in range(2):
+                for (context, px, pw), (pg, pdx, pdw, ptmp) in zip(lanes, extra):
+                    context.conv2d_bwd(px, pw, pg, pdx, pdw, *geom)
+                    context.call("katsu_cuda_add", pg, pg, ptmp, y_count)
+            for context, _, _ in lanes:
+                context.sync()
+            for (context, _, _), (_, pdx, pdw, _), (dx_alone, dw_alone) in zip(lanes, extra, alone):
+                assert np.array_equal(context.download(pdx, x_count), dx_alone)
+                assert np.array_equal(context.download(pdw, w_count), dw_alone)
+    finally:
+        _close(lanes, extra)
