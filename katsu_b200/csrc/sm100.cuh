@@ -150,7 +150,13 @@ __device__ __forceinline__ bool mbar_wait_warp_ready(uint64_t *bar, uint32_t par
     return mbar_wait_warp(bar, parity, status, code);
 }
 
-// Orders generic-proxy writes to shared memory before async-proxy reads (tcgen05.mma, TMA stores).
+// Orders this thread's generic-proxy accesses to shared memory (ld.shared / st.shared) against later
+// async-proxy accesses (tcgen05.mma operand reads, TMA loads and stores).  Needed in both directions:
+//  * after st.shared into a tile that tcgen05.mma or a TMA store will read, before the hand-off arrival;
+//  * after ld.shared from a TMA-written stage, before the arrival that lets TMA refill it.  An mbarrier
+//    arrival alone does not order the refill behind those loads; under memory-system pressure the
+//    refill has been seen to land first, and the loads returned the next tile's data.
+// Stages that only the async proxy reads (TMA -> tcgen05.mma) need no fence; tcgen05.commit orders them.
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
