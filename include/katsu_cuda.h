@@ -76,7 +76,11 @@ int32_t katsu_cuda_free(katsu_cuda_ctx *ctx, float *ptr);
 int32_t katsu_cuda_zero(katsu_cuda_ctx *ctx, float *dst, size_t count);
 /* Explicit host<->device transfer for the device storage variant of
  * TensorNode.data (crates/katsu-core/src/tensor.rs:101-107).  d2h waits for the
- * stream; h2d is ordered on the stream and returns once the source is consumed. */
+ * stream (and, like katsu_cuda_sync, returns KATSU_ERR_TIMEOUT when a bounded
+ * device-side wait gave up in a kernel before it: the data is then undefined).
+ * h2d is ordered on the stream; from pageable memory it returns once the source
+ * has been staged, a page-locked source (katsu_cuda_host_alloc) must stay
+ * untouched until the next katsu_cuda_sync. */
 int32_t katsu_cuda_h2d(katsu_cuda_ctx *ctx, float *dst_device, const float *src_host, size_t count);
 int32_t katsu_cuda_d2h(katsu_cuda_ctx *ctx, float *dst_host, const float *src_device, size_t count);
 /* d2h without the wait: ordered on the stream, dst_host (page-locked) is valid after the
@@ -87,6 +91,8 @@ int32_t katsu_cuda_d2d(katsu_cuda_ctx *ctx, float *dst_device, const float *src_
 /* Page-locked host staging buffers so h2d/d2h run at full PCIe rate. */
 int32_t katsu_cuda_host_alloc(katsu_cuda_ctx *ctx, size_t count, float **out_ptr);
 int32_t katsu_cuda_host_free(katsu_cuda_ctx *ctx, float *ptr);
+/* Waits for everything queued on the context.  KATSU_ERR_TIMEOUT (once) when a bounded
+ * device-side wait gave up in any kernel since the last synchronising call. */
 int32_t katsu_cuda_sync(katsu_cuda_ctx *ctx);
 
 /* ---- Conv2D ------------------------------------------------------------ */
@@ -118,9 +124,9 @@ int32_t katsu_cuda_matmul_fwd(katsu_cuda_ctx *ctx, const float *a, const float *
 /* da[m,k] (+)= g[m,n] @ b^T ; db[k,n] (+)= a^T @ g.  Matmul VJP arm,
  * crates/katsu-core/src/tensor.rs:418-445 (which accumulates into the pending
  * adjoints: pass accumulate != 0 for that behaviour).  da or db may be null.
- * da and db may be the same buffer only when both are square and the caller
- * wants the reference's "same parent, both edges" sum (tensor.rs:425-444): the
- * two products are then applied one after the other. */
+ * da and db may be the same buffer only when m == k == n and the caller wants
+ * the reference's "same parent, both edges" sum (tensor.rs:425-444): the buffer
+ * then receives g @ b^T + a^T @ g (added to its contents when accumulate != 0). */
 int32_t katsu_cuda_matmul_bwd(katsu_cuda_ctx *ctx, const float *a, const float *b, const float *g,
                               float *da, float *db, size_t m, size_t k, size_t n, int32_t accumulate);
 
@@ -140,7 +146,9 @@ int32_t katsu_cuda_sum(katsu_cuda_ctx *ctx, const float *a, float *out, size_t c
  * array is shared by all calls on a device and keeps the last call's partials: calls that
  * overlap on the GPU (other contexts or streams of the same device) race; calls through
  * one context are stream-ordered.  The first call on a device resolves the array's
- * address and should come before any stream capture. */
+ * address and should come before any stream capture, and before the host program's pool
+ * takes the rest of the device memory (the driver may place the library's kernel image on
+ * the device at that first use). */
 #define KATSU_SUM_STATIC_MAX_COUNT ((size_t)1 << 30)
 int32_t katsu_cuda_sum_static(katsu_cuda_ctx *ctx, const float *a, float *out, size_t count);
 /* dst += g : Add VJP edge (tensor.rs:400-408), adjoint accumulation
@@ -163,9 +171,10 @@ int32_t katsu_cuda_allreduce_sum(katsu_cuda_ctx *ctx, float *buf, size_t count);
 
 /* ---- diagnostics (no counterpart in the reference) ------------------------ */
 /* Launches one block that waits, for at most `cycles` SM clocks (1e3..2e8), on a barrier
- * nothing signals.  The wait gives up and the kernel returns; the next katsu_cuda_sync
- * then returns KATSU_ERR_TIMEOUT once and the context remains usable.  Exercises the bounded-
- * wait path of the pipelined kernels without faulting or hanging the device. */
+ * nothing signals.  The wait gives up and the kernel returns; the next synchronising call
+ * (katsu_cuda_sync, katsu_cuda_d2h, katsu_cuda_event_elapsed_ms) then returns
+ * KATSU_ERR_TIMEOUT once and the context remains usable.  Exercises the bounded-wait path of
+ * the pipelined kernels without faulting or hanging the device. */
 int32_t katsu_cuda_selftest_wait_timeout(katsu_cuda_ctx *ctx, uint64_t cycles);
 
 /* ---- timing on the context's stream ------------------------------------ */

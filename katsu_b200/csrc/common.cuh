@@ -26,14 +26,14 @@ struct katsu_cuda_ctx {
     // set by conv2d_bwd while one call computes both dX and dW on the implicit-GEMM path: the dX
     // launch stages g (channels-innermost copy) where the dW launch expects it, once for both
     int share_g_staging, g_staged;
-    // diagnostic: which low-channel tensor-core kernels may be used (bit 0 forward, 1 dX, 2 dW);
-    // from the environment variable KATSU_STEM_TC_MASK at context creation, default all
-    int stem_tc_mask;
     // Buffer written by katsu_cuda_flush_l2.
     float *flush;
     size_t flush_floats;
-    // Device status word for bounded waits (0 = ok).
+    // Device status word for bounded waits (0 = ok) and its page-locked host mirror.
     int *status;
+    int *status_host;
+    // cudaMemPool_t private to the context: katsu_cuda_alloc and the scratch come from it.
+    void *pool;
     // NCCL communicator (void* so this header does not need nccl.h).
     void *comm;
     int comm_ranks;
@@ -52,6 +52,13 @@ int32_t katsu_bind(katsu_cuda_ctx *ctx);
 
 // Ensures ctx->scratch holds at least `floats` floats.
 int32_t katsu_scratch(katsu_cuda_ctx *ctx, size_t floats, float **out);
+
+// Stream-ordered allocation from the context's pool.
+int32_t katsu_pool_alloc(katsu_cuda_ctx *ctx, size_t bytes, void **out);
+
+// cudaStreamSynchronize plus the status word of the bounded device-side waits: KATSU_ERR_TIMEOUT
+// (once; the word is cleared) when a wait gave up in any launch since the last check.
+int32_t katsu_sync_and_check(katsu_cuda_ctx *ctx);
 
 #define KATSU_CUDA_TRY(expr)                                                              \
     do {                                                                                  \

@@ -25,19 +25,52 @@ int32_t katsu_bind(katsu_cuda_ctx *ctx) {
     return KATSU_OK;
 }
 
+int32_t katsu_pool_alloc(katsu_cuda_ctx *ctx, size_t bytes, void **out) {
+    cudaError_t err = ctx->pool != nullptr ? cudaMallocFromPoolAsync(out, bytes, (cudaMemPool_t)ctx->pool, ctx->stream)
+                                           : cudaMallocAsync(out, bytes, ctx->stream);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        *out = nullptr;
+        return katsu_set_error(KATSU_ERR_ALLOC, "stream-ordered allocation of %zu bytes: %s", bytes,
+                               cudaGetErrorString(err));
+    }
+    return KATSU_OK;
+}
+
 int32_t katsu_scratch(katsu_cuda_ctx *ctx, size_t floats, float **out) {
     if (floats > ctx->scratch_floats) {
-        // Earlier launches may still be reading the old block.
-        KATSU_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-        if (ctx->scratch) KATSU_CUDA_TRY(cudaFree(ctx->scratch));
+        // Stream-ordered: launches already queued keep the old block until they have run, and the
+        // new one comes from the context's pool, so growing the scratch does not stall the device.
+        if (ctx->scratch) KATSU_CUDA_TRY(cudaFreeAsync(ctx->scratch, ctx->stream));
         ctx->scratch = nullptr;
         ctx->scratch_floats = 0;
         size_t want = floats < (size_t(1) << 20) ? (size_t(1) << 20) : floats;
-        KATSU_CUDA_TRY(cudaMalloc(&ctx->scratch, want * sizeof(float)));
+        void *p = nullptr;
+        KATSU_TRY(katsu_pool_alloc(ctx, want * sizeof(float), &p));
+        ctx->scratch = (float *)p;
         ctx->scratch_floats = want;
     }
     *out = ctx->scratch;
     return KATSU_OK;
+}
+
+// Reads the status word of the bounded device-side waits after the host has waited for the stream
+// (or for an event behind the kernels in question).  A non-zero word means some wait gave up: the
+// results behind it are undefined, so every synchronising entry point reports it, and the word is
+// cleared so that the context's next launches run normally again.
+static int32_t katsu_report_status(katsu_cuda_ctx *ctx, int status) {
+    if (status == 0) return KATSU_OK;
+    cudaMemsetAsync(ctx->status, 0, sizeof(int), ctx->stream);
+    cudaStreamSynchronize(ctx->stream);
+    return katsu_set_error(KATSU_ERR_TIMEOUT, "a device-side wait gave up (status word %d)", status);
+}
+
+// Waits for the context's stream; the status word travels behind the queued work into a page-locked
+// mirror, so the check costs no second synchronisation.
+int32_t katsu_sync_and_check(katsu_cuda_ctx *ctx) {
+    KATSU_CUDA_TRY(cudaMemcpyAsync(ctx->status_host, ctx->status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    KATSU_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return katsu_report_status(ctx, *ctx->status_host);
 }
 
 extern "C" int32_t katsu_cuda_device_count(int32_t *out_count) {
@@ -74,28 +107,41 @@ extern "C" int32_t katsu_cuda_init(int32_t device, katsu_cuda_ctx **out_ctx) {
     ctx->device = device;
     ctx->num_sms = prop.multiProcessorCount;
     ctx->precision = KATSU_MODE_3XTF32;
-    ctx->stem_tc_mask = 7;
-    if (const char *mask = getenv("KATSU_STEM_TC_MASK")) ctx->stem_tc_mask = atoi(mask) & 7;
-    // katsu_cuda_alloc / katsu_cuda_free are stream-ordered (cudaMallocAsync on the device's
-    // default pool).  Keep freed blocks cached: an autograd step allocates and frees the same
-    // few hundred MB of adjoint buffers every time, and cudaMalloc / cudaFree each cost a
-    // device-wide synchronisation (measured: 34 ms -> a few ms per step of the small CNN).
+    // katsu_cuda_alloc / katsu_cuda_free and the kernels' scratch are stream-ordered allocations
+    // from a pool private to this context that keeps freed blocks cached: an autograd step
+    // allocates and frees the same few hundred MB of adjoint buffers every time, and cudaMalloc /
+    // cudaFree each cost a device-wide synchronisation (measured: 34 ms -> a few ms per step of
+    // the small CNN).  The pool is the context's own, so the host program's other users of the
+    // device's default pool keep their release behaviour; it is destroyed at shutdown.
     {
-        cudaMemPool_t pool;
-        if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
+        cudaMemPoolProps props;
+        memset(&props, 0, sizeof(props));
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = device;
+        cudaMemPool_t pool = nullptr;
+        if (cudaMemPoolCreate(&pool, &props) == cudaSuccess) {
             unsigned long long keep = ~0ull;
             cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+            ctx->pool = pool;
         }
-        cudaGetLastError();
+        cudaGetLastError();  // without a private pool the allocations fall back to cudaMallocAsync's default pool
     }
     err = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (err == cudaSuccess) err = cudaMalloc(&ctx->status, sizeof(int));
+    if (err == cudaSuccess) err = cudaHostAlloc((void **)&ctx->status_host, sizeof(int), cudaHostAllocDefault);
     if (err == cudaSuccess) err = cudaMemsetAsync(ctx->status, 0, sizeof(int), ctx->stream);
     if (err != cudaSuccess) {
+        if (ctx->status_host) cudaFreeHost(ctx->status_host);
+        if (ctx->status) cudaFree(ctx->status);
         if (ctx->stream) cudaStreamDestroy(ctx->stream);
+        if (ctx->pool) cudaMemPoolDestroy((cudaMemPool_t)ctx->pool);
+        cudaGetLastError();
         delete ctx;
         return katsu_set_error(KATSU_ERR_CUDA, "context setup: %s", cudaGetErrorString(err));
     }
+    *ctx->status_host = 0;
     *out_ctx = ctx;
     return KATSU_OK;
 }
@@ -106,10 +152,15 @@ extern "C" int32_t katsu_cuda_shutdown(katsu_cuda_ctx *ctx) {
     KATSU_TRY(katsu_bind(ctx));
     cudaStreamSynchronize(ctx->stream);
     if (ctx->comm) katsu_comm_destroy_impl(ctx);
-    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->scratch) cudaFreeAsync(ctx->scratch, ctx->stream);
+    cudaStreamSynchronize(ctx->stream);
     if (ctx->flush) cudaFree(ctx->flush);
     if (ctx->status) cudaFree(ctx->status);
+    if (ctx->status_host) cudaFreeHost(ctx->status_host);
     cudaStreamDestroy(ctx->stream);
+    // blocks still held by the caller stay valid: the driver releases the pool with its last allocation
+    if (ctx->pool) cudaMemPoolDestroy((cudaMemPool_t)ctx->pool);
+    cudaGetLastError();
     delete ctx;
     return KATSU_OK;
 }
@@ -149,13 +200,8 @@ extern "C" int32_t katsu_cuda_alloc(katsu_cuda_ctx *ctx, size_t count, float **o
     if (count > SIZE_MAX / sizeof(float))
         return katsu_set_error(KATSU_ERR_ALLOC, "allocation of %zu floats overflows", count);
     float *p = nullptr;
-    cudaError_t err = cudaMallocAsync(&p, count * sizeof(float), ctx->stream);
-    if (err != cudaSuccess) {
-        cudaGetLastError();
-        return katsu_set_error(KATSU_ERR_ALLOC, "cudaMallocAsync(%zu bytes): %s", count * sizeof(float),
-                               cudaGetErrorString(err));
-    }
-    err = cudaMemsetAsync(p, 0, count * sizeof(float), ctx->stream);
+    KATSU_TRY(katsu_pool_alloc(ctx, count * sizeof(float), (void **)&p));
+    cudaError_t err = cudaMemsetAsync(p, 0, count * sizeof(float), ctx->stream);
     if (err != cudaSuccess) {
         cudaFreeAsync(p, ctx->stream);
         return katsu_set_error(KATSU_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(err));
@@ -197,8 +243,8 @@ extern "C" int32_t katsu_cuda_d2h(katsu_cuda_ctx *ctx, float *dst_host, const fl
         KATSU_CUDA_TRY(cudaMemcpyAsync(dst_host, src_device, count * sizeof(float), cudaMemcpyDeviceToHost,
                                        ctx->stream));
     }
-    KATSU_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-    return KATSU_OK;
+    // the data is only as good as the kernels that produced it: a wait that gave up is reported here too
+    return katsu_sync_and_check(ctx);
 }
 
 extern "C" int32_t katsu_cuda_d2h_async(katsu_cuda_ctx *ctx, float *dst_host, const float *src_device, size_t count) {
@@ -243,14 +289,7 @@ extern "C" int32_t katsu_cuda_host_free(katsu_cuda_ctx *ctx, float *ptr) {
 
 extern "C" int32_t katsu_cuda_sync(katsu_cuda_ctx *ctx) {
     KATSU_TRY(katsu_bind(ctx));
-    KATSU_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-    int status = 0;
-    KATSU_CUDA_TRY(cudaMemcpy(&status, ctx->status, sizeof(int), cudaMemcpyDeviceToHost));
-    if (status != 0) {
-        cudaMemset(ctx->status, 0, sizeof(int));
-        return katsu_set_error(KATSU_ERR_TIMEOUT, "a device-side wait gave up (status word %d)", status);
-    }
-    return KATSU_OK;
+    return katsu_sync_and_check(ctx);
 }
 
 // ---- timing ----------------------------------------------------------------
@@ -288,7 +327,11 @@ extern "C" int32_t katsu_cuda_event_elapsed_ms(katsu_cuda_ctx *ctx, katsu_cuda_e
     KATSU_TRY(katsu_bind(ctx));
     KATSU_CUDA_TRY(cudaEventSynchronize(stop->ev));
     KATSU_CUDA_TRY(cudaEventElapsedTime(out_ms, start->ev, stop->ev));
-    return KATSU_OK;
+    // The kernels in front of `stop` have run: a time measured over a wait that gave up is not a
+    // measurement.  The word is read directly (work queued behind `stop` may still be running).
+    int status = 0;
+    KATSU_CUDA_TRY(cudaMemcpy(&status, ctx->status, sizeof(int), cudaMemcpyDeviceToHost));
+    return katsu_report_status(ctx, status);
 }
 
 extern "C" int32_t katsu_cuda_event_destroy(katsu_cuda_ctx *ctx, katsu_cuda_event *event) {

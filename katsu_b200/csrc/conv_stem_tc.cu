@@ -32,10 +32,6 @@
 
 using namespace sm100;
 
-#define KATSU_PROF_ARRAY g_katsu_role_prof
-#define KATSU_PROF_READER katsu_debug_role_prof
-#include "role_prof.cuh"
-
 namespace {
 
 struct StemDims {
@@ -142,11 +138,9 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
         const int group = (warp - 4 * GROUPS) >> 2;
         const int r = (warp & 3) * 32 + lane;
         const int win = (r >> 5) * 40 + (r & 31) + 3;  // window origin (ky = kx = 0) inside a channel's 6x40 tile
-        PROF_DECL
         for (int it = group; it < my_tiles; it += GROUPS) {
             const int s = it % AS, xs = it % XS;
             if (!mbar_wait_warp_ready(&x_full[xs], (it / XS) & 1, d.status, 45)) break;
-            PROF_MARK(0)
             float v[32];
             const float *xt = x_tiles[xs] + win;
 #pragma unroll
@@ -162,10 +156,8 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(&x_empty[xs]);
-            PROF_MARK(1)
             if (it >= AS && !mbar_wait_warp_ready(&empty[s], ((it / AS) - 1) & 1, d.status, 41)) break;
             tc_fence_after_sync();
-            PROF_MARK(2)
             const uint32_t a_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + a_col0 + uint32_t(s) * 64;
             float lo[32];
 #pragma unroll
@@ -179,9 +171,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
             tmem_st_wait();
             tc_fence_before_sync();
             mbar_arrive(&full[s]);  // every thread, after its own tcgen05.wait::st
-            PROF_MARK(3)
         }
-        if (r == 0 && group == 0) PROF_DUMP(0)
     } else if (warp == TMA_WARP && lane == 0) {
         // ---- TMA loads of the x halo tiles ----
         for (int it = 0; it < my_tiles; ++it) {
@@ -205,13 +195,10 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
             db_hi[j] = smem_desc(smem_u32(b_hi) + j * 32, 16, 1024, kLayoutSw128);
             db_lo[j] = smem_desc(smem_u32(b_lo) + j * 32, 16, 1024, kLayoutSw128);
         }
-        PROF_DECL
         for (int it = 0; it < my_tiles; ++it) {
             const int s = it % AS, b = it % NB;
             if (!mbar_wait_warp_ready(&full[s], (it / AS) & 1, d.status, 42)) break;
-            PROF_MARK(0)
             if (it >= NB && !mbar_wait_warp_ready(&acc_empty[b], ((it / NB) - 1) & 1, d.status, 43)) break;
-            PROF_MARK(1)
             tc_fence_after_sync();
             const uint32_t acc = tmem_base + uint32_t(b) * d.np;
             const uint32_t a_hi = tmem_base + a_col0 + uint32_t(s) * 64, a_lo = a_hi + 32;
@@ -232,9 +219,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
                 mma_commit(&acc_full[b]);
             }
             __syncwarp();
-            PROF_MARK(2)
         }
-        if (lane == 0) PROF_DUMP(1)
     } else if (warp < 4 * GROUPS) {
         // ---- epilogue: TMEM -> registers (thread = pixel) -> shared staging [oc][4 rows][32 px]
         // -> global with 128-bit stores (a warp writes the four 128-byte row segments of one
@@ -244,7 +229,6 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
         const int r = quarter * 32 + lane;
         const int bar_id = 1 + group;
         float *stage = out_stages + group * (64 * 128);
-        PROF_DECL
         bool alive = true;
         for (int it = group; it < my_tiles; it += GROUPS) {
             const int b = it % NB;
@@ -253,7 +237,6 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
             // has failed all later waits return at once, so the rest of the loop is quick.
             if (alive) alive = mbar_wait_warp_ready(&acc_full[b], (it / NB) & 1, d.status, 44);
             tc_fence_after_sync();
-            PROF_MARK(0)
             const int tile = blockIdx.x + it * gridDim.x;
             const int img = tile / tiles_per_img, tt = tile % tiles_per_img;
             const int oy0 = (tt / d.tiles_x) * 4, ox0 = (tt % d.tiles_x) * 32;
@@ -272,9 +255,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
                     tc_fence_before_sync();
                     mbar_arrive(&acc_empty[b]);  // every thread, after its own tcgen05.wait::ld
                 }
-                PROF_MARK(1)
                 named_barrier(bar_id, 128);
-                PROF_MARK(2)
                 const int chans = !alive ? 0 : (d.k - c0) < 64 ? (d.k - c0) : 64;
                 for (int f = r; f < chans * 32; f += 128) {
                     const int oc = f >> 5, row = (f >> 3) & 3, col = (f & 7) * 4;
@@ -284,10 +265,8 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
                         __stcs(reinterpret_cast<float4 *>(y + (size_t(img) * d.k + c0 + oc) * plane + size_t(oy) * d.w + ox), q);
                     }
                 }
-                PROF_MARK(3)
             }
         }
-        if (r == 0 && group == 0) PROF_DUMP(2)
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -346,7 +325,6 @@ int32_t katsu_conv_stem_tc_fwd(katsu_cuda_ctx *ctx, const float *x, const float 
                                size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
                                size_t stride, size_t pad, int *handled) {
     *handled = 0;
-    if (!(ctx->stem_tc_mask & 1)) return KATSU_OK;
     if (!stem_tc_shape(ctx, n, c, h, wd, k, r, s, stride, pad)) return KATSU_OK;
     if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0 || (reinterpret_cast<uintptr_t>(y) & 15u) != 0) return KATSU_OK;
     *handled = 1;

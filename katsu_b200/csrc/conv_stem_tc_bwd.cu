@@ -30,10 +30,6 @@
 
 using namespace sm100;
 
-#define KATSU_PROF_ARRAY g_katsu_role_prof_bwd
-#define KATSU_PROF_READER katsu_debug_role_prof_bwd
-#include "role_prof.cuh"
-
 namespace {
 
 __device__ __forceinline__ float tf32_hi(float v) { return __uint_as_float(__float_as_uint(v) & 0xFFFFE000u); }
@@ -47,6 +43,7 @@ struct StemDxDims {
     int tiles_x, tiles_y;   // 28-column, 14-row output tiles
     int chunks;             // 16-oc chunks of g per tile
     int kblocks;            // 32-oc blocks of the filter operand
+    int gs;                 // g stages in shared memory (DX_GS, or fewer when the filter operand is large)
     int three_pass;
     int accumulate;
     int *status;
@@ -57,7 +54,7 @@ constexpr int DX_RW = 32, DX_RH = 16;          // g region that is multiplied (o
 constexpr int DX_GW = 36;                      // g columns TMA loads per row (region starts at column 3)
 constexpr int DX_OC = 16;                      // oc per chunk
 constexpr int DX_GSTAGE = DX_OC * DX_RH * DX_GW;  // floats per g stage
-constexpr int DX_GS = 4;                       // g stages
+constexpr int DX_GS = 4;                       // g stages at most (StemDxDims::gs of them are used)
 constexpr int DX_ZP = DX_RW * DX_RH;           // pixels per Z plane
 constexpr int DX_THREADS = 15 * 32;
 
@@ -76,7 +73,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
     unsigned char *b_hi = smem;
     unsigned char *b_lo = b_hi + d.kblocks * 4096;
     float *g_stages = reinterpret_cast<float *>(b_lo + d.kblocks * 4096);
-    float *zs = g_stages + DX_GS * DX_GSTAGE;
+    float *zs = g_stages + d.gs * DX_GSTAGE;
     float *outs = zs + TAPS * DX_ZP;
     __shared__ uint64_t g_full[DX_GS], g_empty[DX_GS], a_full[2], a_empty[2], d_full[2], d_empty[2];
     __shared__ uint32_t tmem_slot;
@@ -84,7 +81,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
     const int tiles_per_img = d.tiles_x * d.tiles_y;
     const int total_tiles = d.n * tiles_per_img;
     const int my_tiles = (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int NCH = d.chunks;
+    const int NCH = d.chunks, GS = d.gs;
 
     if (tid == 0) {
         for (int s = 0; s < DX_GS; ++s) {
@@ -126,13 +123,11 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
     if (warp >= 4 && warp < 12) {
         // ---- builders: thread = one pixel of two M-tiles; 16 oc per chunk -> TMEM A (hi | lo) ----
         const int quarter = warp & 3, half = (warp - 4) >> 2;
-        PROF_DECL
         for (int it = 0; it < my_tiles; ++it) {
             bool ok = true;
             for (int q = 0; q < NCH; ++q) {
-                const int cc = it * NCH + q, gs = cc % DX_GS, as = cc & 1;
-                if (!mbar_wait_warp_ready(&g_full[gs], (cc / DX_GS) & 1, d.status, 61)) { ok = false; break; }
-                PROF_MARK(0)
+                const int cc = it * NCH + q, gs = cc % GS, as = cc & 1;
+                if (!mbar_wait_warp_ready(&g_full[gs], (cc / GS) & 1, d.status, 61)) { ok = false; break; }
                 const float *st = g_stages + gs * DX_GSTAGE + 3 + lane;
                 float v[2][32];
 #pragma unroll
@@ -149,21 +144,17 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
                 fence_proxy_async_smem();  // ordinary reads of the stage before its TMA refill
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&g_empty[gs]);
-                PROF_MARK(1)
                 if (cc >= 2 && !mbar_wait_warp_ready(&a_empty[as], ((cc >> 1) - 1) & 1, d.status, 62)) { ok = false; break; }
                 tc_fence_after_sync();
-                PROF_MARK(2)
                 const uint32_t a_addr = tmem_base + (uint32_t(quarter * 32) << 16) + A_COL0 + uint32_t(as) * 128 + uint32_t(2 * half) * 32;
                 tmem_st_32x32(a_addr, v[0]);
                 tmem_st_32x32(a_addr + 32, v[1]);
                 tmem_st_wait();
                 tc_fence_before_sync();
                 mbar_arrive(&a_full[as]);
-                PROF_MARK(3)
             }
             if (!ok) break;
         }
-        if (tid == 128) PROF_DUMP(0)
     } else if (warp == 14 && lane == 0) {
         // ---- TMA loads of the g chunks ----
         for (int it = 0; it < my_tiles; ++it) {
@@ -172,8 +163,8 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
             const int x0 = (tt % d.tiles_x) * DX_TW, y0 = (tt / d.tiles_x) * DX_TH;
             bool ok = true;
             for (int q = 0; q < NCH; ++q) {
-                const int cc = it * NCH + q, gs = cc % DX_GS;
-                if (cc >= DX_GS && !mbar_wait(&g_empty[gs], ((cc / DX_GS) - 1) & 1, d.status, 63)) { ok = false; break; }
+                const int cc = it * NCH + q, gs = cc % GS;
+                if (cc >= GS && !mbar_wait(&g_empty[gs], ((cc / GS) - 1) & 1, d.status, 63)) { ok = false; break; }
                 mbar_arrive_expect_tx(&g_full[gs], DX_GSTAGE * 4);
                 tma_load_4d(g_stages + gs * DX_GSTAGE, &map_g, &g_full[gs], x0 - 4, y0 - 1, q * DX_OC, img);
             }
@@ -189,17 +180,14 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
         const uint32_t idesc = idesc_tf32(128, 32, false, false);
         const uint64_t db_hi0 = smem_desc(smem_u32(b_hi), 16, 1024, kLayoutSw128);
         const uint64_t db_lo0 = smem_desc(smem_u32(b_lo), 16, 1024, kLayoutSw128);
-        PROF_DECL
         for (int it = 0; it < my_tiles; ++it) {
             const int db = it & 1;
             bool ok = true;
             for (int q = 0; q < NCH; ++q) {
                 const int cc = it * NCH + q, as = cc & 1;
                 if (!mbar_wait_warp_ready(&a_full[as], (cc >> 1) & 1, d.status, 64)) { ok = false; break; }
-                PROF_MARK(0)
                 if (q == 0 && it >= 2 && !mbar_wait_warp_ready(&d_empty[db], ((it >> 1) - 1) & 1, d.status, 65)) { ok = false; break; }
                 tc_fence_after_sync();
-                PROF_MARK(1)
 #pragma unroll
                 for (int m = 0; m < 2; ++m) {
                     const int j = 2 * mw + m;
@@ -225,17 +213,14 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
                     if (q == NCH - 1) mma_commit(&d_full[db]);
                 }
                 __syncwarp();
-                PROF_MARK(2)
             }
             if (!ok) break;
         }
-        if (mw == 0 && lane == 0) PROF_DUMP(1)
     } else if (warp < 4) {
         // ---- epilogue: Z out of TMEM into [tap][pixel] planes, col2im gather, TMA store ----
         const int quarter = warp;
         const size_t plane = size_t(d.h) * d.w;
         bool alive = true;
-        PROF_DECL
         for (int it = 0; it < my_tiles; ++it) {
             const int db = it & 1;
             // A warp whose wait ran out keeps meeting the others at the named barriers (they may
@@ -243,7 +228,6 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
             // failed all later waits return at once, so the rest of the loop is quick.
             if (alive) alive = mbar_wait_warp_ready(&d_full[db], (it >> 1) & 1, d.status, 66);
             tc_fence_after_sync();
-            PROF_MARK(0)
             const int tile = blockIdx.x + it * gridDim.x;
             const int img = tile / tiles_per_img, tt = tile % tiles_per_img;
             const int x0 = (tt % d.tiles_x) * DX_TW, y0 = (tt / d.tiles_x) * DX_TH;
@@ -261,7 +245,6 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
             }
             if (tid == 0) tma_store_wait_read<0>();  // the previous tile's store has read `outs`
             named_barrier(1, 128);
-            PROF_MARK(1)
             if (alive && lane < DX_TW) {
                 for (int iy = warp; iy < DX_TH; iy += 4) {
                     const float *zr = zs + (iy + 2) * DX_RW + lane + 2;
@@ -283,18 +266,34 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
             }
             fence_proxy_async_smem();
             named_barrier(1, 128);
-            PROF_MARK(2)
             if (tid == 0 && alive) {
                 tma_store_4d(&map_dx, outs, x0, y0, 0, img);
                 tma_store_commit();
             }
         }
-        if (tid == 0) PROF_DUMP(2)
         if (tid == 0) tma_store_wait_all<0>();
     }
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 12) tmem_dealloc(tmem_base, 512);
+}
+
+// Dynamic shared memory of the dX kernel with `gs` g stages.
+template <int CIN>
+size_t dx_smem_bytes(int kblocks, int gs) {
+    return size_t(kblocks) * 8192 + size_t(gs) * DX_GSTAGE * 4 + size_t(CIN) * 9 * DX_ZP * 4 +
+           size_t(CIN) * DX_TH * DX_TW * 4 + 1024;
+}
+
+// The most g stages (4, else 3) whose shared-memory request the SM can grant; 0 when neither fits
+// (the caller then uses the CUDA-core kernel).  Three channels with more than 64 output channels
+// need 233 056 B with four stages, above the 232 448 B a block may opt in to.
+template <int CIN>
+int dx_stages(int kblocks) {
+    constexpr size_t kMaxOptIn = 232448 - 256;  // the kernel's barriers are static shared memory
+    for (int gs = DX_GS; gs >= 3; --gs)
+        if (dx_smem_bytes<CIN>(kblocks, gs) <= kMaxOptIn) return gs;
+    return 0;
 }
 
 template <int CIN>
@@ -314,8 +313,7 @@ int32_t dx_launch(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx
         if (!katsu_make_tensor_map(&map_dx, dx, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
             return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (stem dX out)");
     }
-    const size_t smem = size_t(d.kblocks) * 8192 + size_t(DX_GS) * DX_GSTAGE * 4 + size_t(CIN) * 9 * DX_ZP * 4 +
-                        size_t(CIN) * DX_TH * DX_TW * 4 + 1024;
+    const size_t smem = dx_smem_bytes<CIN>(d.kblocks, d.gs);
     auto kernel = stem_dx_tc_kernel<CIN>;
     KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const size_t total_tiles = size_t(d.n) * d.tiles_x * d.tiles_y;
@@ -432,13 +430,11 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
             mbar_arrive(&d_empty);
             return true;
         };
-        PROF_DECL
         bool ok = true;
         for (int kb = group; kb < my_kblocks; kb += 2) {
             if (group == 0 && kb > 0 && kb % DW_DRAIN == 0 && !drain(kb / DW_DRAIN - 1)) { ok = false; break; }
             const int gs = kb % DW_GS, as = kb % DW_AS;
             if (!mbar_wait_warp_ready(&g_full[gs], (kb / DW_GS) & 1, d.status, 71)) { ok = false; break; }
-            PROF_MARK(0)
             const unsigned char *grow = g_stages + gs * 8192 + oc * 128;
             float v[32];
 #pragma unroll
@@ -460,17 +456,13 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
             fence_proxy_async_smem();  // ordinary reads of the stage before its TMA refill
             __syncwarp();
             if (lane == 0) mbar_arrive(&g_empty[gs]);
-            PROF_MARK(1)
             if (kb >= DW_AS && !mbar_wait_warp_ready(&ab_empty[as], ((kb / DW_AS) - 1) & 1, d.status, 72)) { ok = false; break; }
             tc_fence_after_sync();
-            PROF_MARK(2)
             tmem_st_32x32(lane_addr + DW_A_COL0 + uint32_t(as) * 32, v);
             tmem_st_wait();
             tc_fence_before_sync();
             mbar_arrive(&ab_full[as]);
-            PROF_MARK(3)
         }
-        if (tid == 0) PROF_DUMP(0)
         if (group == 0) {
             if (ok) drain((my_kblocks - 1) / DW_DRAIN);
             // combine the hi rows with the lo rows of the same oc and write this block's partial
@@ -494,11 +486,9 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
             off_hi[kx] = t * 128 + ((j ^ (t & 7)) << 4);
         }
         const int src_off = (c * 6 + ky) * 40 + 4 * j + 3;
-        PROF_DECL
         for (int it = 0; it < my_tiles; ++it) {
             const int xs = it % DW_XS;
             if (!mbar_wait_warp_ready(&x_full[xs], (it / DW_XS) & 1, d.status, 74)) break;
-            PROF_MARK(0)
             bool ok = true;
             for (int r = 0; r < 4; ++r) {
                 const int kb = it * 4 + r, bs = kb % DW_BS;
@@ -510,9 +500,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
                     f[1] = q.x; f[2] = q.y; f[3] = q.z; f[4] = q.w;
                     f[5] = ld_shared_f32(src + 5);
                 }
-                PROF_MARK(1)
                 if (kb >= DW_BS && !mbar_wait_warp_ready(&ab_empty[bs], ((kb / DW_BS) - 1) & 1, d.status, 75)) { ok = false; break; }
-                PROF_MARK(2)
                 if (active) {
                     unsigned char *bt = b_stages + bs * 8192;
                     float lo[6];
@@ -526,28 +514,23 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(&ab_full[bs]);
-                PROF_MARK(3)
             }
             if (!ok) break;
             fence_proxy_async_smem();  // ordinary reads of the stage before its TMA refill
             __syncwarp();
             if (lane == 0) mbar_arrive(&x_empty[xs]);
         }
-        if (tid == 256) PROF_DUMP(1)
     } else if (warp == DW_MMA_WARP) {
         // ---- MMA issue (whole warp runs the loop, the elected thread issues) ----
         const bool issue = elect_one();
         const uint32_t idesc = idesc_tf32(128, 64, false, false);
         const uint64_t bdesc0 = smem_desc(smem_u32(b_stages), 16, 1024, kLayoutSw128);
-        PROF_DECL
         for (int kb = 0; kb < my_kblocks; ++kb) {
             const int as = kb % DW_AS, bs = kb % DW_BS;
             if (!mbar_wait_warp_ready(&ab_full[as], (kb / DW_AS) & 1, d.status, 76)) break;
-            PROF_MARK(0)
             const int period = kb / DW_DRAIN, in_period = kb - period * DW_DRAIN;
             if (in_period == 0 && period > 0 && !mbar_wait_warp_ready(&d_empty, (period - 1) & 1, d.status, 78)) break;
             tc_fence_after_sync();
-            PROF_MARK(1)
             const uint32_t acc = tmem_base + uint32_t(kb & 1) * 64;
             const uint32_t a_addr = tmem_base + DW_A_COL0 + uint32_t(as) * 32;
             const uint64_t bdesc = bdesc0 + uint64_t((bs * 8192) >> 4);
@@ -559,9 +542,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
                 if (in_period == DW_DRAIN - 1 || kb + 1 == my_kblocks) mma_commit(&d_full);
             }
             __syncwarp();
-            PROF_MARK(2)
         }
-        if (lane == 0) PROF_DUMP(2)
     } else if (lane == 0) {
         // ---- TMA loads: one x halo tile per 4-row tile, one g row segment per K-block ----
         for (int it = 0; it < my_tiles; ++it) {
@@ -648,7 +629,7 @@ int32_t dw_launch(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw
 int32_t katsu_conv_stem_tc_dx(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx, size_t n, size_t c,
                               size_t h, size_t wd, size_t k, int accumulate, int *handled) {
     *handled = 0;
-    if (ctx->precision == KATSU_MODE_FP32 || !(ctx->stem_tc_mask & 2)) return KATSU_OK;
+    if (ctx->precision == KATSU_MODE_FP32) return KATSU_OK;
     if (c < 1 || c > 3 || k < 1 || k > 128 || h > 32768 || wd > 32768 || wd % 4 != 0) return KATSU_OK;
     if ((reinterpret_cast<uintptr_t>(g) & 15u) != 0 || (reinterpret_cast<uintptr_t>(dx) & 15u) != 0) return KATSU_OK;
     StemDxDims d;
@@ -661,6 +642,8 @@ int32_t katsu_conv_stem_tc_dx(katsu_cuda_ctx *ctx, const float *w, const float *
     d.three_pass = ctx->precision == KATSU_MODE_3XTF32 ? 1 : 0;
     d.accumulate = accumulate;
     d.status = ctx->status;
+    d.gs = c == 1 ? dx_stages<1>(d.kblocks) : c == 2 ? dx_stages<2>(d.kblocks) : dx_stages<3>(d.kblocks);
+    if (d.gs == 0) return KATSU_OK;
     *handled = 1;
     switch (c) {
         case 1: return dx_launch<1>(ctx, w, g, dx, d);
@@ -672,7 +655,7 @@ int32_t katsu_conv_stem_tc_dx(katsu_cuda_ctx *ctx, const float *w, const float *
 int32_t katsu_conv_stem_tc_dw(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw, size_t n, size_t c,
                               size_t h, size_t wd, size_t k, int accumulate, int *handled) {
     *handled = 0;
-    if (ctx->precision == KATSU_MODE_FP32 || !(ctx->stem_tc_mask & 4)) return KATSU_OK;
+    if (ctx->precision == KATSU_MODE_FP32) return KATSU_OK;
     if (c < 1 || c > 3 || k < 1 || k > 64 || n == 0 || h > 32768 || wd > 32768 || wd % 4 != 0) return KATSU_OK;
     if ((reinterpret_cast<uintptr_t>(g) & 15u) != 0 || (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return KATSU_OK;
     StemDwDims d;

@@ -389,6 +389,9 @@ extern "C" int32_t katsu_cuda_matmul_bwd(katsu_cuda_ctx *ctx, const float *a, co
     }
     KATSU_REQUIRE(a != nullptr && b != nullptr && g != nullptr, "null operand");
     const bool skinny = skinny_shape(m, k, n);
+    // da == db (the reference's "same parent on both edges", tensor.rs:425-444, possible when
+    // m == k == n): the second product is added to the first whatever `accumulate` says.
+    const int accumulate_db = (da != nullptr && da == db) ? 1 : accumulate;
     if (da != nullptr) {
         if (skinny) {
 #define CALL(NP) skinny_da<NP>(ctx, g, b, da, m, k, n, accumulate)
@@ -404,15 +407,15 @@ extern "C" int32_t katsu_cuda_matmul_bwd(katsu_cuda_ctx *ctx, const float *a, co
     }
     if (db != nullptr) {
         if (skinny) {
-#define CALL(NP) skinny_db<NP>(ctx, a, g, db, m, k, n, accumulate)
+#define CALL(NP) skinny_db<NP>(ctx, a, g, db, m, k, n, accumulate_db)
             int32_t rc = [&]() -> int32_t { KATSU_NP_SWITCH(n, CALL); }();
 #undef CALL
             KATSU_TRY(rc);
         } else {
             // db[k,n] = a^T @ g : A(i,p)=a[p*k+i], B(p,j)=g[p*n+j]  (both MN-major for the tensor cores)
             int handled = 0;
-            KATSU_TRY(katsu_umma_gemm(ctx, a, g, db, k, n, m, true, true, accumulate, &handled));
-            if (!handled) KATSU_TRY(gemm_strided(ctx, a, g, db, k, n, m, 1, k, n, 1, accumulate));
+            KATSU_TRY(katsu_umma_gemm(ctx, a, g, db, k, n, m, true, true, accumulate_db, &handled));
+            if (!handled) KATSU_TRY(gemm_strided(ctx, a, g, db, k, n, m, 1, k, n, 1, accumulate_db));
         }
     }
     return KATSU_OK;

@@ -110,9 +110,6 @@ __device__ __forceinline__ bool mbar_wait_budget(uint64_t *bar, uint32_t parity,
     const long long start = clock64();
     for (uint32_t i = 0; i < kWaitPolls; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-#ifdef KATSU_WAIT_SLEEP
-        __nanosleep(KATSU_WAIT_SLEEP);
-#endif
         if ((i & 63u) == 63u) {
             // once any wait of the launch has given up, the others follow at once instead of
             // each running out its own budget

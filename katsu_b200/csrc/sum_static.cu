@@ -3,10 +3,11 @@
 // Who that is: a host program whose device memory is handed out entirely by
 // its own pool (a framework allocator that has reserved all of HBM, so a
 // cudaMalloc made behind its back fails), and latency-sensitive loops that
-// cannot accept the device-wide synchronisation cudaMalloc / cudaFree imply.
-// katsu_cuda_sum grows the context's scratch block with cudaMalloc on demand;
-// this variant keeps its per-block partial sums in a fixed array that is part
-// of the library image instead, so it calls no cudaMalloc, cudaFree or any
+// cannot accept an allocation of any kind on their path.
+// katsu_cuda_sum takes its partials from the context's scratch block, which
+// grows on demand with an allocation from the context's memory pool; this
+// variant keeps its per-block partial sums in a fixed array that is part of
+// the library image instead, so it calls no cudaMalloc, cudaFree or any
 // other allocating routine, ever.
 //
 // Cost and limits: every GPU that loads the library holds the 16 KiB array
@@ -18,7 +19,10 @@
 // context are ordered by its stream and are safe.
 //
 // The first call on a device looks up the array's device address (a host-side
-// lookup, no allocation); make that first call before any stream capture.
+// lookup, no allocation by this library); make that first call before any
+// stream capture, and before the host program's pool reserves whatever device
+// memory is left: the driver loads the library's kernels onto the device at
+// their first use and may take memory for the module image then.
 #include "common.cuh"
 
 namespace {

@@ -84,18 +84,13 @@ def _draw(dist, seed, count):
 
 def conv_inputs(spec: ConvSpec, first_image: int = 0, images: int | None = None):
     """(x, w) as flat f32 arrays.  `first_image`/`images` select a batch shard
-    without generating the rest (the uniform stream is counter based; normal
-    draws are generated whole and sliced)."""
+    without generating the rest (both streams are counter based)."""
     images = spec.n - first_image if images is None else images
     per_image = spec.c * spec.h * spec.w
     if spec.x_dist[0] == "uniform":
-        bits = synth.splitmix_u24(spec.x_seed, images * per_image, offset=first_image * per_image)
-        u = bits.astype(np.float32) / np.float32(16777216.0)
-        lo, hi = spec.x_dist[1], spec.x_dist[2]
-        x = (np.float32(lo) + np.float32(hi - lo) * u).astype(np.float32)
+        x = synth.uniform(spec.x_seed, images * per_image, spec.x_dist[1], spec.x_dist[2], offset=first_image * per_image)
     else:
-        full = _draw(spec.x_dist, spec.x_seed, spec.n * per_image)
-        x = full[first_image * per_image:(first_image + images) * per_image].copy()
+        x = synth.normal(spec.x_seed, images * per_image, spec.x_dist[1], offset=first_image * per_image)
     w = _draw(spec.w_dist, spec.w_seed, spec.k * spec.c * spec.r * spec.s)
     return x, w
 

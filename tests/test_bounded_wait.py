@@ -27,3 +27,28 @@ def test_budget_outside_the_allowed_range_is_refused(ctx):
     with pytest.raises(cabi.KatsuCudaError) as info:
         ctx.call("katsu_cuda_selftest_wait_timeout", 10)
     assert info.value.code == cabi.ERR_INVALID_ARG
+
+
+def test_download_after_a_wait_that_gave_up_reports_it_too(ctx):
+    """A caller that fetches results with katsu_cuda_d2h alone (never calling katsu_cuda_sync) must
+    not receive the output of a launch whose wait ran out as if it were good."""
+    with DeviceArrays(ctx, a=np.ones(16, np.float32)) as d:
+        ctx.sync()
+        ctx.call("katsu_cuda_selftest_wait_timeout", 2_000_000)
+        with pytest.raises(cabi.KatsuCudaError) as info:
+            d.get("a")
+        assert info.value.code == cabi.ERR_TIMEOUT
+        assert np.all(d.get("a") == 1.0)  # reported once; the context is re-armed
+
+
+def test_elapsed_time_over_a_wait_that_gave_up_is_refused(ctx):
+    ctx.sync()
+    start, stop = ctx.event(), ctx.event()
+    ctx.record(start)
+    ctx.call("katsu_cuda_selftest_wait_timeout", 2_000_000)
+    ctx.record(stop)
+    with pytest.raises(cabi.KatsuCudaError) as info:
+        ctx.elapsed_ms(start, stop)
+    assert info.value.code == cabi.ERR_TIMEOUT
+    ctx.sync()
+    ctx.event_destroy(start), ctx.event_destroy(stop)

@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 import make_golden  # noqa: E402
 
-from parity_util import REL_L2_TOL, DeviceArrays, rel_l2  # noqa: E402
+from parity_util import DeviceArrays, assert_parity  # noqa: E402
 
 GOLDEN = np.load(os.path.join(HERE, "golden", "conv_matmul_golden.npz"))
 
@@ -64,8 +64,9 @@ def test_device_matches_conv_golden(ctx, name):
         d.alloc("y", GOLDEN[f"conv/{name}/y"].size), d.alloc("dx", x.size), d.alloc("dw", wt.size)
         ctx.conv2d_fwd(d["x"], d["w"], d["y"], n, c, h, w, k, r, s, stride, pad)
         ctx.conv2d_bwd(d["x"], d["w"], d["g"], d["dx"], d["dw"], n, c, h, w, k, r, s, stride, pad, 0)
-        for key in ("y", "dx", "dw"):
-            assert rel_l2(d.get(key), GOLDEN[f"conv/{name}/{key}"]) <= REL_L2_TOL, key
+        oh, ow = (h + 2 * pad - r) // stride + 1, (w + 2 * pad - s) // stride + 1
+        for key, terms in (("y", c * r * s), ("dx", k * r * s), ("dw", n * oh * ow)):
+            assert_parity(d.get(key), GOLDEN[f"conv/{name}/{key}"], terms, what=(name, key))
 
 
 @pytest.mark.gpu
@@ -77,8 +78,8 @@ def test_device_matches_matmul_golden(ctx, name):
         d.alloc("c", m * n), d.alloc("da", m * k), d.alloc("db", k * n)
         ctx.matmul_fwd(d["a"], d["b"], d["c"], m, k, n)
         ctx.matmul_bwd(d["a"], d["b"], d["g"], d["da"], d["db"], m, k, n, 0)
-        for key in ("c", "da", "db"):
-            assert rel_l2(d.get(key), GOLDEN[f"matmul/{name}/{key}"]) <= REL_L2_TOL, key
+        for key, terms in (("c", k), ("da", n), ("db", m)):
+            assert_parity(d.get(key), GOLDEN[f"matmul/{name}/{key}"], terms, what=(name, key))
 
 
 @pytest.mark.gpu

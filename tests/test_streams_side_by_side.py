@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 
 from katsu_b200 import cabi, workloads
+from parity_util import assert_parity
 
 pytestmark = pytest.mark.gpu
 
@@ -32,7 +33,7 @@ def _close(lanes, extra):
         context.close()
 
 
-def test_forward_beside_other_streams_is_bit_identical():
+def test_forward_beside_other_streams_is_bit_identical(oracle):
     spec = workloads.CONV["stem_256x3x224"].with_batch(16)
     geom = (spec.n, spec.c, spec.h, spec.w, spec.k, spec.r, spec.s, spec.stride, spec.pad)
     y_count = spec.n * spec.k * spec.oh * spec.ow
@@ -44,6 +45,14 @@ def test_forward_beside_other_streams_is_bit_identical():
         context.sync()
         alone.append(context.download(py, y_count).copy())
         extra.append((py, pg))
+    # "alone" is itself held to the oracle (sampled elements, reference visiting order), so that a
+    # defect which shows with and without neighbours cannot pass as bit-identical
+    x, w = workloads.conv_inputs(spec)
+    idx = np.random.default_rng(3).integers(0, y_count, 4000)
+    for i, y_alone in enumerate(alone):
+        xi = (x * np.float32(i + 1)).astype(np.float32)
+        y32, _ = oracle.sample_y(xi, w, idx, spec.x_shape, spec.w_shape, spec.stride, spec.pad)
+        assert_parity(y_alone[idx], y32, spec.c * 9, what=("forward alone", i))
     try:
         for _ in range(REPEATS):
             for _ in range(3):
@@ -58,7 +67,7 @@ def test_forward_beside_other_streams_is_bit_identical():
         _close(lanes, extra)
 
 
-def test_backward_beside_other_streams_is_bit_identical():
+def test_backward_beside_other_streams_is_bit_identical(oracle):
     spec = workloads.CONV["stem_256x3x224"].with_batch(16)
     geom = (spec.n, spec.c, spec.h, spec.w, spec.k, spec.r, spec.s, spec.stride, spec.pad)
     x_count = spec.n * spec.c * spec.h * spec.w
@@ -74,6 +83,15 @@ def test_backward_beside_other_streams_is_bit_identical():
         context.sync()
         alone.append((context.download(pdx, x_count).copy(), context.download(pdw, w_count).copy()))
         extra.append((pg, pdx, pdw, ptmp))
+    x, w = workloads.conv_inputs(spec)
+    idx_x = np.random.default_rng(4).integers(0, x_count, 4000)
+    idx_w = np.random.default_rng(5).choice(w_count, 64, replace=False)
+    for i, (dx_alone, dw_alone) in enumerate(alone):
+        xi = (x * np.float32(i + 1)).astype(np.float32)
+        _, dx64 = oracle.sample_dx(w, g, idx_x, spec.x_shape, spec.w_shape, spec.stride, spec.pad)
+        _, dw64 = oracle.sample_dw(xi, g, idx_w, spec.x_shape, spec.w_shape, spec.stride, spec.pad)
+        assert_parity(dx_alone[idx_x], dx64, spec.k * 9, what=("dX alone", i))
+        assert_parity(dw_alone[idx_w], dw64, spec.n * spec.oh * spec.ow, what=("dW alone", i))
     try:
         for _ in range(REPEATS):
             for _ in range(2):

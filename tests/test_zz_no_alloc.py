@@ -38,6 +38,36 @@ def test_static_scratch_sum_matches_allocating_sum_twice_in_a_row(ctx):
         assert float(d.get("out")[0]) == 0.0
 
 
+def test_static_scratch_sum_reads_an_unaligned_input(ctx):
+    """An input that does not start on a 16-byte boundary takes the kernel's scalar loads."""
+    rng = np.random.default_rng(43)
+    host = rng.standard_normal(3_000_001).astype(np.float32)
+    with DeviceArrays(ctx, a=host) as d:
+        d.alloc("out", 1, fill=np.nan)
+        for skip in (1, 3):
+            ctx.call("katsu_cuda_sum_static", d["a"] + 4 * skip, d["out"], host.size - skip)
+            exact = float(np.sum(host[skip:].astype(np.float64)))
+            scale = float(np.sum(np.abs(host[skip:].astype(np.float64))))
+            assert abs(float(d.get("out")[0]) - exact) <= 1e-6 * scale, skip
+
+
+def test_static_scratch_sum_leaves_free_device_memory_unchanged(ctx):
+    """After its first call on the device (address lookup, kernels loaded) a call takes no device
+    memory: the free byte count the driver reports is the same before and after."""
+    torch = pytest.importorskip("torch")
+    host = np.ones(1 << 20, np.float32)
+    with DeviceArrays(ctx, a=host) as d:
+        d.alloc("out", 1, fill=np.nan)
+        ctx.call("katsu_cuda_sum_static", d["a"], d["out"], host.size)  # first use on this device
+        ctx.sync()
+        free_before, _ = torch.cuda.mem_get_info(0)
+        ctx.call("katsu_cuda_sum_static", d["a"], d["out"], host.size)
+        ctx.sync()
+        free_after, _ = torch.cuda.mem_get_info(0)
+        assert float(d.get("out")[0]) == float(host.size)
+    assert free_after == free_before, (free_before, free_after)
+
+
 def test_static_scratch_sum_refuses_sizes_beyond_its_maximum(ctx):
     with DeviceArrays(ctx, a=np.ones(8, np.float32)) as d:
         d.alloc("out", 1, fill=3.0)
