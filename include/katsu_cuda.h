@@ -116,6 +116,34 @@ int32_t katsu_cuda_conv2d_bwd(katsu_cuda_ctx *ctx, const float *x, const float *
                               size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
                               size_t stride, size_t pad, int32_t accumulate);
 
+/* One backward_buffers (conv2d.rs:269-292) whose upstream gradient is gfactor * gscale[0] * g[i]
+ * without that product ever being stored: gscale is a device scalar (null: 1).  The VJP of
+ * loss = sum(y * y) hands the convolution exactly this, g = y with gfactor = 2 and gscale = the
+ * adjoint of the loss (crates/katsu-core/src/tensor.rs:392-417), so the backward pass reads y where
+ * it would otherwise write and re-read a gradient of y's size.  dX and dW are linear in the upstream
+ * gradient; kernels that support it scale their outputs, others get the scaled gradient written
+ * out once internally.  Same aliasing and accumulate rules as katsu_cuda_conv2d_bwd. */
+int32_t katsu_cuda_conv2d_bwd_scaled(katsu_cuda_ctx *ctx, const float *x, const float *w, const float *g,
+                                     const float *gscale, float gfactor, float *dx, float *dw,
+                                     size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                                     size_t stride, size_t pad, int32_t accumulate);
+/* y = act(conv(x, w) + bias[k]) with act = max(., 0) when relu != 0; bias may be null.  Bias and
+ * ReLU are not in the reference yet (docs/roadmap.md:18-26 lists them as the next layer features);
+ * here they ride in the convolution kernel's epilogue where it has one, so a layer's activation
+ * costs no extra pass over y. */
+int32_t katsu_cuda_conv2d_fwd_bias_relu(katsu_cuda_ctx *ctx, const float *x, const float *w, const float *bias,
+                                        float *y, size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r,
+                                        size_t s, size_t stride, size_t pad, int32_t relu);
+/* Backward of that epilogue over y_act [n, k, plane]: dg = g where y_act > 0 else 0 (relu != 0;
+ * dg may alias g, or be null when only dbias is wanted), dbias[k] (+)= sum over n and the plane of
+ * dg (null: skipped).  With relu == 0 the gradient passes through unchanged: pass dg = null and
+ * feed g to katsu_cuda_conv2d_bwd. */
+int32_t katsu_cuda_bias_relu_bwd(katsu_cuda_ctx *ctx, const float *y_act, const float *g, float *dg, float *dbias,
+                                 size_t n, size_t k, size_t plane, int32_t relu, int32_t accumulate_bias);
+/* w[i] -= lr * dw[i], the plain SGD update the roadmap names (docs/roadmap.md:21-22), so that a
+ * training step's parameters never leave the device. */
+int32_t katsu_cuda_sgd_step(katsu_cuda_ctx *ctx, float *w, const float *dw, float lr, size_t count);
+
 /* ---- matmul ------------------------------------------------------------ */
 /* c[m,n] = a[m,k] @ b[k,n]; Tensor::matmul, crates/katsu-core/src/tensor.rs:264-273.
  * c is fully overwritten (zero when k == 0). */
@@ -151,6 +179,16 @@ int32_t katsu_cuda_sum(katsu_cuda_ctx *ctx, const float *a, float *out, size_t c
  * the device at that first use). */
 #define KATSU_SUM_STATIC_MAX_COUNT ((size_t)1 << 30)
 int32_t katsu_cuda_sum_static(katsu_cuda_ctx *ctx, const float *a, float *out, size_t count);
+/* out[0] = sum_i a[i] * a[i]: Tensor::mul(a, a) followed by Tensor::sum (tensor.rs:226-247) in one
+ * pass over a, every square rounded to f32 before it is added (as the product tensor would hold
+ * it) and the same summation tree as katsu_cuda_sum, so the result equals the two-step one bit for
+ * bit while the product tensor is never written. */
+int32_t katsu_cuda_sumsq(katsu_cuda_ctx *ctx, const float *a, float *out, size_t count);
+/* dst[i] (+)= s[0]*src[i] + s[0]*src[i]: both Mul VJP edges of q = y * y (tensor.rs:392-409) when
+ * the adjoint of q is the broadcast of one device scalar s[0] (what the Sum VJP produces,
+ * tensor.rs:410-417), without that broadcast being stored. */
+int32_t katsu_cuda_square_vjp(katsu_cuda_ctx *ctx, float *dst, const float *src, const float *s, size_t count,
+                              int32_t accumulate);
 /* dst += g : Add VJP edge (tensor.rs:400-408), adjoint accumulation
  * (tensor.rs:387-389) and gradient publication (tensor.rs:353-356). */
 int32_t katsu_cuda_axpy_acc(katsu_cuda_ctx *ctx, float *dst, const float *g, size_t count);

@@ -25,6 +25,7 @@ __all__ = [
     "Tensor", "Conv2D", "Op", "TensorError", "ShapeOverflow", "InvalidConv", "MissingForward",
     "NonScalarBackward", "GradientBorrowed", "DataLength", "ShapeMismatch", "RankMismatch",
     "MatmulMismatch", "Allocation", "DeviceError", "set_device", "set_precision", "synchronize",
+    "set_loss_fusion", "loss_fusion",
     "context", "MODE_3XTF32", "MODE_TF32", "MODE_FP32",
 ]
 
@@ -143,6 +144,9 @@ def _load():
             "kh_tensor_reshape": [_vp, _szp, _sz, ctypes.POINTER(_vp)],
             "kh_tensor_backward": [_vp], "kh_tensor_backward_with": [_vp, _vp, _sz],
             "kh_tensor_to_device": [_vp], "kh_tensor_to_host": [_vp],
+            "kh_tensor_sgd_step": [_vp, ctypes.c_float],
+            "kh_conv_from_weights_bias": [_vp, _vp, _sz, _sz, ctypes.c_int, ctypes.POINTER(_vp)],
+            "kh_conv_bias": [_vp, ctypes.POINTER(_vp)], "kh_conv_relu": [_vp], "kh_loss_fusion": [],
             "kh_tensor_device_data": [_vp, ctypes.POINTER(_vp)], "kh_tensor_device_grad": [_vp, ctypes.POINTER(_vp)],
             "kh_conv_new_seeded": [_sz, _sz, _sz, _sz, _sz, _sz, ctypes.c_uint64, ctypes.POINTER(_vp)],
             "kh_conv_from_weights": [_vp, _sz, _sz, ctypes.POINTER(_vp)],
@@ -160,7 +164,8 @@ def _load():
             ("kh_tensor_op", [_vp, ctypes.POINTER(ctypes.c_int), _szp, _szp], None),
             ("kh_tensor_parent_count", [_vp], _sz), ("kh_grad_borrow_release", [_vp], None),
             ("kh_conv_free", [_vp], None), ("kh_conv_stride", [_vp], _sz), ("kh_conv_padding", [_vp], _sz),
-            ("kh_conv_clear_cache", [_vp], None),
+            ("kh_conv_clear_cache", [_vp], None), ("kh_set_loss_fusion", [ctypes.c_int], None),
+            ("kh_tensor_op_flags", [_vp, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)], None),
         ]:
             fn = getattr(lib, name)
             fn.argtypes, fn.restype = argtypes, restype
@@ -198,6 +203,17 @@ def synchronize() -> None:
     _check(_load().kh_synchronize())
 
 
+def set_loss_fusion(on: bool) -> None:
+    """Loss-graph fusion (default on): y.mul(y) defers its values, sum() of it reads y once, and
+    backward hands the convolution "2 * s * y" symbolically instead of writing it out.  Values and
+    gradients are those of node-by-node evaluation (tensor.rs:226-247, 392-417) either way."""
+    _load().kh_set_loss_fusion(1 if on else 0)
+
+
+def loss_fusion() -> bool:
+    return bool(_load().kh_loss_fusion())
+
+
 def context() -> int:
     """The raw katsu_cuda_ctx* the host mirror uses (for C-ABI level callers)."""
     out = _vp()
@@ -211,24 +227,28 @@ def context() -> int:
 class Op:
     _KINDS = ["Leaf", "Add", "Mul", "Matmul", "Conv2D", "Sum", "Reshape"]
 
-    def __init__(self, kind, stride=None, padding=None):
-        self.kind, self.stride, self.padding = kind, stride, padding
+    def __init__(self, kind, stride=None, padding=None, bias=False, relu=False):
+        self.kind, self.stride, self.padding, self.bias, self.relu = kind, stride, padding, bias, relu
+
+    def _key(self):
+        return (self.kind, self.stride, self.padding, self.bias, self.relu)
 
     def __eq__(self, other):
-        return isinstance(other, Op) and (self.kind, self.stride, self.padding) == (
-            other.kind, other.stride, other.padding)
+        return isinstance(other, Op) and self._key() == other._key()
 
     def __hash__(self):
-        return hash((self.kind, self.stride, self.padding))
+        return hash(self._key())
 
     def __repr__(self):
         if self.kind == "Conv2D":
-            return f"Conv2D {{ stride: {self.stride}, padding: {self.padding} }}"
+            extra = (", bias" if self.bias else "") + (", relu" if self.relu else "")
+            return f"Conv2D {{ stride: {self.stride}, padding: {self.padding}{extra} }}"
         return self.kind
 
     @staticmethod
-    def Conv2D(stride, padding):
-        return Op("Conv2D", stride, padding)
+    def Conv2D(stride, padding, bias=False, relu=False):
+        """bias / relu are additions (the reference's roadmap lists them as not implemented yet)."""
+        return Op("Conv2D", stride, padding, bias, relu)
 
 
 Op.Leaf, Op.Add, Op.Mul, Op.Matmul, Op.Sum, Op.Reshape = (
@@ -318,7 +338,11 @@ class Tensor:
         kind, stride, padding = ctypes.c_int(), _sz(), _sz()
         _lib.kh_tensor_op(self._h, ctypes.byref(kind), ctypes.byref(stride), ctypes.byref(padding))
         name = Op._KINDS[kind.value]
-        return Op.Conv2D(stride.value, padding.value) if name == "Conv2D" else Op(name)
+        if name != "Conv2D":
+            return Op(name)
+        bias, relu = ctypes.c_int(), ctypes.c_int()
+        _lib.kh_tensor_op_flags(self._h, ctypes.byref(bias), ctypes.byref(relu))
+        return Op.Conv2D(stride.value, padding.value, bool(bias.value), bool(relu.value))
 
     def parents(self):
         result = []
@@ -376,6 +400,10 @@ class Tensor:
         seed = np.ascontiguousarray(np.asarray(seed, dtype=np.float32).reshape(-1))
         _check(_lib.kh_tensor_backward_with(self._h, seed.ctypes.data, seed.size))
 
+    def sgd_step(self, lr):
+        """Addition (docs/roadmap.md:21-22): data -= lr * grad in place on the device."""
+        _check(_lib.kh_tensor_sgd_step(self._h, float(lr)))
+
     def to_device(self):
         _check(_lib.kh_tensor_to_device(self._h))
         return self
@@ -413,12 +441,26 @@ class Conv2D:
         return cls(in_channels, out_channels, kernel_size, stride, padding, seed)
 
     @classmethod
-    def from_weights(cls, weights, stride, padding):
+    def from_weights(cls, weights, stride, padding, bias=None, relu=False):
+        """bias (a rank-1 Tensor, one value per output channel) and relu are additions: they run in
+        the convolution kernel's epilogue and take part in autograd as a third parent of the node."""
         out = _vp()
-        _check(_load().kh_conv_from_weights(weights._h, stride, padding, ctypes.byref(out)))
+        if bias is None and not relu:
+            _check(_load().kh_conv_from_weights(weights._h, stride, padding, ctypes.byref(out)))
+        else:
+            _check(_load().kh_conv_from_weights_bias(weights._h, bias._h if bias is not None else None, stride,
+                                                     padding, 1 if relu else 0, ctypes.byref(out)))
         layer = cls.__new__(cls)
         layer._h = out.value
         return layer
+
+    def bias(self):
+        out = _vp()
+        _check(_lib.kh_conv_bias(self._h, ctypes.byref(out)))
+        return Tensor._wrap(out.value) if out.value else None
+
+    def relu(self):
+        return bool(_lib.kh_conv_relu(self._h))
 
     def __del__(self):
         h = getattr(self, "_h", None)

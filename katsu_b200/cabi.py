@@ -48,6 +48,12 @@ SIGNATURES = {
     "katsu_cuda_sync": [_ctx],
     "katsu_cuda_conv2d_fwd": [_ctx, _ptr, _ptr, _ptr] + [_sz] * 9,
     "katsu_cuda_conv2d_bwd": [_ctx, _ptr, _ptr, _ptr, _ptr, _ptr] + [_sz] * 9 + [_i32],
+    "katsu_cuda_conv2d_bwd_scaled": [_ctx, _ptr, _ptr, _ptr, _ptr, ctypes.c_float, _ptr, _ptr] + [_sz] * 9 + [_i32],
+    "katsu_cuda_conv2d_fwd_bias_relu": [_ctx, _ptr, _ptr, _ptr, _ptr] + [_sz] * 9 + [_i32],
+    "katsu_cuda_bias_relu_bwd": [_ctx, _ptr, _ptr, _ptr, _ptr, _sz, _sz, _sz, _i32, _i32],
+    "katsu_cuda_sgd_step": [_ctx, _ptr, _ptr, ctypes.c_float, _sz],
+    "katsu_cuda_sumsq": [_ctx, _ptr, _ptr, _sz],
+    "katsu_cuda_square_vjp": [_ctx, _ptr, _ptr, _ptr, _sz, _i32],
     "katsu_cuda_matmul_fwd": [_ctx, _ptr, _ptr, _ptr, _sz, _sz, _sz],
     "katsu_cuda_matmul_bwd": [_ctx, _ptr, _ptr, _ptr, _ptr, _ptr, _sz, _sz, _sz, _i32],
     "katsu_cuda_add": [_ctx, _ptr, _ptr, _ptr, _sz],

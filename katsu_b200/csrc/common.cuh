@@ -148,17 +148,30 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *g,
                             size_t stride, size_t pad, size_t oh, size_t ow, int accumulate, int *handled);
 
 // Low-channel (C <= 3) 3x3 stride-1 pad-1 convolution on the tensor cores (conv_stem_tc.cu).
+// bias (may be null) and relu are applied in the kernel's epilogue.
 int32_t katsu_conv_stem_tc_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,
                                size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
-                               size_t stride, size_t pad, int *handled);
+                               size_t stride, size_t pad, const float *bias, int relu, int *handled);
+
+// y = act(y + bias[channel]) in place (streaming.cu), for the convolution kernels without a fused epilogue.
+int32_t katsu_bias_relu_inplace(katsu_cuda_ctx *ctx, float *y, const float *bias, size_t n, size_t k, size_t plane,
+                                int relu);
 
 // dX of the same shape family on the tensor cores (conv_stem_tc_bwd.cu); *handled = 0 in FP32
 // mode or when TMA cannot describe the tensors.
+// The upstream gradient is gfactor * gscale[0] * g (gscale: device scalar or null for 1); the kernels
+// apply the factor to their outputs, so g itself is only read.
 int32_t katsu_conv_stem_tc_dx(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx, size_t n, size_t c,
-                              size_t h, size_t wd, size_t k, int accumulate, int *handled);
+                              size_t h, size_t wd, size_t k, int accumulate, const float *gscale, float gfactor,
+                              int *handled);
 
 int32_t katsu_conv_stem_tc_dw(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw, size_t n, size_t c,
-                              size_t h, size_t wd, size_t k, int accumulate, int *handled);
+                              size_t h, size_t wd, size_t k, int accumulate, const float *gscale, float gfactor,
+                              int *handled);
+
+// True when those two kernels take every output this backward call asks for.
+bool katsu_conv_stem_tc_bwd_takes(const katsu_cuda_ctx *ctx, const float *x, const float *g, const float *dx,
+                                  const float *dw, size_t n, size_t c, size_t h, size_t wd, size_t k);
 
 // TMA-fed dX stencil (conv_stencil_tma.cu); *handled = 0 when TMA cannot describe g.
 int32_t katsu_stencil_dx_tma(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx, size_t n, size_t c,
@@ -175,4 +188,5 @@ int32_t katsu_conv_stencil_fwd(katsu_cuda_ctx *ctx, const float *x, const float 
 int32_t katsu_conv_stencil_bwd(katsu_cuda_ctx *ctx, const float *x, const float *w, const float *g,
                                float *dx, float *dw,
                                size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
-                               size_t stride, size_t pad, int accumulate, int *handled);
+                               size_t stride, size_t pad, int accumulate, const float *gscale, float gfactor,
+                               int *handled);

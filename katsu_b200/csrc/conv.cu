@@ -28,28 +28,46 @@ int32_t geometry(size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s, si
 
 }  // namespace
 
-extern "C" int32_t katsu_cuda_conv2d_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,
-                                         size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
-                                         size_t stride, size_t pad) {
+namespace {
+
+int32_t forward(katsu_cuda_ctx *ctx, const float *x, const float *w, const float *bias, float *y,
+                size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s, size_t stride, size_t pad,
+                int relu) {
     KATSU_TRY(katsu_bind(ctx));
     Geometry g;
     KATSU_TRY(geometry(c, h, wd, k, r, s, stride, pad, &g));
     if (n == 0) return KATSU_OK;  // empty batch: y has no elements (conv2d.rs:195-196)
     KATSU_REQUIRE(x != nullptr && w != nullptr && y != nullptr, "null tensor");
     int handled = 0;
-    KATSU_TRY(katsu_conv_stem_tc_fwd(ctx, x, w, y, n, c, h, wd, k, r, s, stride, pad, &handled));
-    if (handled) return KATSU_OK;
+    KATSU_TRY(katsu_conv_stem_tc_fwd(ctx, x, w, y, n, c, h, wd, k, r, s, stride, pad, bias, relu, &handled));
+    if (handled) return KATSU_OK;  // bias and ReLU were applied in that kernel's epilogue
     KATSU_TRY(katsu_conv_stencil_fwd(ctx, x, w, y, n, c, h, wd, k, r, s, stride, pad, &handled));
-    if (handled) return KATSU_OK;
-    KATSU_TRY(katsu_conv_igemm_fwd(ctx, x, w, y, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow, &handled));
-    if (handled) return KATSU_OK;
-    return katsu_conv_direct_fwd(ctx, x, w, y, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow);
+    if (!handled) KATSU_TRY(katsu_conv_igemm_fwd(ctx, x, w, y, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow, &handled));
+    if (!handled) KATSU_TRY(katsu_conv_direct_fwd(ctx, x, w, y, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow));
+    return katsu_bias_relu_inplace(ctx, y, bias, n, k, g.oh * g.ow, relu);
 }
 
-extern "C" int32_t katsu_cuda_conv2d_bwd(katsu_cuda_ctx *ctx, const float *x, const float *w, const float *gr,
-                                         float *dx, float *dw,
-                                         size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
-                                         size_t stride, size_t pad, int32_t accumulate) {
+// out[i] = factor * fl(s[0] * in[i]): the scaled upstream gradient written out, for the kernels that
+// cannot apply the scale themselves.
+__global__ void __launch_bounds__(256) scale_copy_kernel(float *__restrict__ out, const float *__restrict__ in,
+                                                         const float *__restrict__ s, float factor, size_t count) {
+    const float scalar = s != nullptr ? __ldg(s) : 1.f;
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride)
+        out[i] = factor * __fmul_rn(scalar, in[i]);
+}
+
+int32_t scale_copy(katsu_cuda_ctx *ctx, float *out, const float *in, const float *s, float factor, size_t count) {
+    size_t blocks = katsu_div_up(count, 256);
+    if (blocks > size_t(ctx->num_sms) * 8) blocks = size_t(ctx->num_sms) * 8;
+    KATSU_LAUNCH(ctx, scale_copy_kernel, (unsigned)blocks, 256, 0, out, in, s, factor, count);
+    return KATSU_OK;
+}
+
+int32_t backward(katsu_cuda_ctx *ctx, const float *x, const float *w, const float *gr, const float *gscale,
+                 float gfactor, float *dx, float *dw,
+                 size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s, size_t stride, size_t pad,
+                 int32_t accumulate) {
     KATSU_TRY(katsu_bind(ctx));
     Geometry g;
     KATSU_TRY(geometry(c, h, wd, k, r, s, stride, pad, &g));
@@ -64,9 +82,21 @@ extern "C" int32_t katsu_cuda_conv2d_bwd(katsu_cuda_ctx *ctx, const float *x, co
     KATSU_REQUIRE(dx == nullptr || w != nullptr, "dx needs the weights");
     KATSU_REQUIRE(dw == nullptr || x != nullptr, "dw needs the input");
     int handled = 0;
-    KATSU_TRY(katsu_conv_stencil_bwd(ctx, x, w, gr, dx, dw, n, c, h, wd, k, r, s, stride, pad, accumulate,
-                                     &handled));
+    KATSU_TRY(katsu_conv_stencil_bwd(ctx, x, w, gr, dx, dw, n, c, h, wd, k, r, s, stride, pad, accumulate, gscale,
+                                     gfactor, &handled));
     if (handled) return KATSU_OK;
+    if (gscale != nullptr || gfactor != 1.f) {
+        // no kernel for this shape applies the scale itself: write the scaled gradient out once
+        const size_t count = n * k * g.oh * g.ow;
+        void *scaled = nullptr;
+        KATSU_TRY(katsu_pool_alloc(ctx, count * sizeof(float), &scaled));
+        int32_t rc = scale_copy(ctx, (float *)scaled, gr, gscale, gfactor, count);
+        if (rc == KATSU_OK)
+            rc = backward(ctx, x, w, (const float *)scaled, nullptr, 1.f, dx, dw, n, c, h, wd, k, r, s, stride, pad,
+                          accumulate);
+        cudaFreeAsync(scaled, ctx->stream);
+        return rc;
+    }
     ctx->share_g_staging = (dx != nullptr && dw != nullptr) ? 1 : 0;
     ctx->g_staged = 0;
     if (dx != nullptr) {
@@ -81,4 +111,32 @@ extern "C" int32_t katsu_cuda_conv2d_bwd(katsu_cuda_ctx *ctx, const float *x, co
     }
     ctx->share_g_staging = ctx->g_staged = 0;
     return KATSU_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t katsu_cuda_conv2d_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,
+                                         size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                                         size_t stride, size_t pad) {
+    return forward(ctx, x, w, nullptr, y, n, c, h, wd, k, r, s, stride, pad, 0);
+}
+
+extern "C" int32_t katsu_cuda_conv2d_fwd_bias_relu(katsu_cuda_ctx *ctx, const float *x, const float *w, const float *bias,
+                                                   float *y, size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r,
+                                                   size_t s, size_t stride, size_t pad, int32_t relu) {
+    return forward(ctx, x, w, bias, y, n, c, h, wd, k, r, s, stride, pad, relu ? 1 : 0);
+}
+
+extern "C" int32_t katsu_cuda_conv2d_bwd(katsu_cuda_ctx *ctx, const float *x, const float *w, const float *gr,
+                                         float *dx, float *dw,
+                                         size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                                         size_t stride, size_t pad, int32_t accumulate) {
+    return backward(ctx, x, w, gr, nullptr, 1.f, dx, dw, n, c, h, wd, k, r, s, stride, pad, accumulate);
+}
+
+extern "C" int32_t katsu_cuda_conv2d_bwd_scaled(katsu_cuda_ctx *ctx, const float *x, const float *w, const float *gr,
+                                                const float *gscale, float gfactor, float *dx, float *dw,
+                                                size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                                                size_t stride, size_t pad, int32_t accumulate) {
+    return backward(ctx, x, w, gr, gscale, gfactor, dx, dw, n, c, h, wd, k, r, s, stride, pad, accumulate);
 }

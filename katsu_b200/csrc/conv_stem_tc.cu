@@ -42,6 +42,8 @@ struct StemDims {
     int a_stages;            // 2 or 3 stages of the A tile
     int acc_buffers;         // 2 or 4 TMEM accumulators
     int *status;
+    const float *bias;       // optional per-output-channel bias added in the epilogue (null: none)
+    int relu;                // epilogue clamps at zero
 };
 
 __device__ __forceinline__ float tf32_hi(float v) { return __uint_as_float(__float_as_uint(v) & 0xFFFFE000u); }
@@ -86,10 +88,13 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
     __shared__ __align__(128) float x_tiles[XS][XT];                   // [c][6 rows][40 columns]
     __shared__ uint64_t full[3], empty[3], acc_full[4], acc_empty[4], x_full[XS], x_empty[XS];
     __shared__ uint32_t tmem_slot;
+    __shared__ float bias_s[128];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles_per_img = d.tiles_x * d.tiles_y;
     const int total_tiles = d.n * tiles_per_img;
     const int my_tiles = (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const bool post_op = d.bias != nullptr || d.relu != 0;
+    if (tid < 128) bias_s[tid] = (d.bias != nullptr && tid < d.k) ? __ldg(d.bias + tid) : 0.f;
     uint32_t tmem_cols = 32;
     while ((int)tmem_cols < NB * d.np + AS * 64) tmem_cols <<= 1;
     const uint32_t a_col0 = uint32_t(NB * d.np);  // first column of the A stages
@@ -247,6 +252,13 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
                     if (alive && c0 + 32 * h < d.np) {
                         float v[32];
                         tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + b * d.np + c0 + 32 * h, v);
+                        if (post_op) {  // bias and ReLU fused behind the accumulator (block-uniform branch)
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                v[i] += bias_s[c0 + 32 * h + i];
+                                if (d.relu) v[i] = fmaxf(v[i], 0.f);
+                            }
+                        }
 #pragma unroll
                         for (int i = 0; i < 32; ++i) st_shared_f32(stage + (32 * h + i) * 128 + r, v[i]);
                     }
@@ -323,7 +335,7 @@ int32_t fwd_launch(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y
 
 int32_t katsu_conv_stem_tc_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,
                                size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
-                               size_t stride, size_t pad, int *handled) {
+                               size_t stride, size_t pad, const float *bias, int relu, int *handled) {
     *handled = 0;
     if (!stem_tc_shape(ctx, n, c, h, wd, k, r, s, stride, pad)) return KATSU_OK;
     if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0 || (reinterpret_cast<uintptr_t>(y) & 15u) != 0) return KATSU_OK;
@@ -335,6 +347,8 @@ int32_t katsu_conv_stem_tc_fwd(katsu_cuda_ctx *ctx, const float *x, const float 
     d.np = (int)katsu_div_up(k, 32) * 32;
     d.three_pass = ctx->precision == KATSU_MODE_3XTF32 ? 1 : 0;
     d.status = ctx->status;
+    d.bias = bias;
+    d.relu = relu;
     switch (c) {
         case 1: return fwd_launch<1>(ctx, x, w, y, d);
         case 2: return fwd_launch<2>(ctx, x, w, y, d);

@@ -47,6 +47,10 @@ struct StemDxDims {
     int three_pass;
     int accumulate;
     int *status;
+    // The upstream gradient is gfactor * gscale[0] * g (gscale may be null: 1).  dX is linear in it,
+    // so the factor is applied once per output element in the epilogue.
+    const float *gscale;
+    float gfactor;
 };
 
 constexpr int DX_TW = 28, DX_TH = 14;          // output tile
@@ -220,6 +224,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
         // ---- epilogue: Z out of TMEM into [tap][pixel] planes, col2im gather, TMA store ----
         const int quarter = warp;
         const size_t plane = size_t(d.h) * d.w;
+        const float alpha = d.gfactor * (d.gscale != nullptr ? __ldg(d.gscale) : 1.f);
         bool alive = true;
         for (int it = 0; it < my_tiles; ++it) {
             const int db = it & 1;
@@ -256,6 +261,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
 #pragma unroll
                             for (int kx = 0; kx < 3; ++kx)
                                 acc += ld_shared_f32(zr + ((c * 3 + ky) * 3 + kx) * DX_ZP - ky * DX_RW - kx);
+                        acc *= alpha;
                         if (d.accumulate) {
                             const int gy = y0 + iy, gx = x0 + lane;
                             if (gy < d.h && gx < d.w) acc = dx[(size_t(img) * CIN + c) * plane + size_t(gy) * d.w + gx] + acc;
@@ -573,7 +579,8 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
 // reproducible) with eight loads per element in flight instead of one (21 -> a few microseconds,
 // which matters when a GPU's share of the batch makes the whole kernel 100 microseconds).
 __global__ void __launch_bounds__(256)
-stem_dw_fold_kernel(const float *__restrict__ partial, float *dw, int elems, int parts, int accumulate) {
+stem_dw_fold_kernel(const float *__restrict__ partial, float *dw, int elems, int parts, int accumulate,
+                    const float *__restrict__ gscale, float gfactor) {
     __shared__ float sums[8][32];
     const int i = blockIdx.x * 32 + (threadIdx.x & 31), part = threadIdx.x >> 5;
     float s = 0.f;
@@ -585,12 +592,14 @@ stem_dw_fold_kernel(const float *__restrict__ partial, float *dw, int elems, int
         float total = sums[0][threadIdx.x];
 #pragma unroll
         for (int q = 1; q < 8; ++q) total += sums[q][threadIdx.x];
+        total *= gfactor * (gscale != nullptr ? __ldg(gscale) : 1.f);  // dW is linear in the upstream gradient
         dw[i] = accumulate ? dw[i] + total : total;
     }
 }
 
 template <int CIN>
-int32_t dw_launch(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw, StemDwDims d, int accumulate) {
+int32_t dw_launch(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw, StemDwDims d, int accumulate,
+                  const float *gscale, float gfactor) {
     CUtensorMap map_g, map_x;
     {
         const uint64_t dims[4] = {(uint64_t)d.w, (uint64_t)d.h, (uint64_t)d.k, (uint64_t)d.n};
@@ -620,30 +629,62 @@ int32_t dw_launch(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw
     KATSU_TRY(katsu_scratch(ctx, grid * elems, &partial));
     KATSU_LAUNCH(ctx, kernel, (unsigned)grid, DW_THREADS, smem, map_g, map_x, partial, d);
     KATSU_LAUNCH(ctx, stem_dw_fold_kernel, (unsigned)katsu_div_up((size_t)elems, (size_t)32), 256, 0, partial, dw, elems,
-                 (int)grid, accumulate);
+                 (int)grid, accumulate, gscale, gfactor);
     return KATSU_OK;
 }
 
 }  // namespace
 
+namespace {
+
+int dx_stages_for(size_t c, int kblocks) {
+    return c == 1 ? dx_stages<1>(kblocks) : c == 2 ? dx_stages<2>(kblocks) : dx_stages<3>(kblocks);
+}
+
+bool dx_takes(const katsu_cuda_ctx *ctx, const float *g, const float *dx, size_t n, size_t c, size_t h, size_t wd,
+              size_t k) {
+    if (ctx->precision == KATSU_MODE_FP32) return false;
+    if (c < 1 || c > 3 || k < 1 || k > 128 || h > 32768 || wd > 32768 || wd % 4 != 0) return false;
+    if ((reinterpret_cast<uintptr_t>(g) & 15u) != 0 || (reinterpret_cast<uintptr_t>(dx) & 15u) != 0) return false;
+    if (n * katsu_div_up(wd, DX_TW) * katsu_div_up(h, DX_TH) > 0x3fffffffu / 8) return false;  // chunk counters stay in int
+    return katsu_tensor_map_encoder() != nullptr && dx_stages_for(c, (int)katsu_div_up(k, 32)) != 0;
+}
+
+bool dw_takes(const katsu_cuda_ctx *ctx, const float *x, const float *g, size_t n, size_t c, size_t h, size_t wd,
+              size_t k) {
+    if (ctx->precision == KATSU_MODE_FP32) return false;
+    if (c < 1 || c > 3 || k < 1 || k > 64 || n == 0 || h > 32768 || wd > 32768 || wd % 4 != 0) return false;
+    if ((reinterpret_cast<uintptr_t>(g) & 15u) != 0 || (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return false;
+    if (n * katsu_div_up(wd, 32) * katsu_div_up(h, 4) > 0x3fffffffu / 4) return false;  // K-block counters stay in int
+    return katsu_tensor_map_encoder() != nullptr;
+}
+
+}  // namespace
+
+// Whether the tensor-core kernels below take this backward call (the outputs that are asked for);
+// they apply a scale on the upstream gradient themselves, other kernels need it materialised.
+bool katsu_conv_stem_tc_bwd_takes(const katsu_cuda_ctx *ctx, const float *x, const float *g, const float *dx,
+                                  const float *dw, size_t n, size_t c, size_t h, size_t wd, size_t k) {
+    return (dx == nullptr || dx_takes(ctx, g, dx, n, c, h, wd, k)) && (dw == nullptr || dw_takes(ctx, x, g, n, c, h, wd, k));
+}
+
 int32_t katsu_conv_stem_tc_dx(katsu_cuda_ctx *ctx, const float *w, const float *g, float *dx, size_t n, size_t c,
-                              size_t h, size_t wd, size_t k, int accumulate, int *handled) {
+                              size_t h, size_t wd, size_t k, int accumulate, const float *gscale, float gfactor,
+                              int *handled) {
     *handled = 0;
-    if (ctx->precision == KATSU_MODE_FP32) return KATSU_OK;
-    if (c < 1 || c > 3 || k < 1 || k > 128 || h > 32768 || wd > 32768 || wd % 4 != 0) return KATSU_OK;
-    if ((reinterpret_cast<uintptr_t>(g) & 15u) != 0 || (reinterpret_cast<uintptr_t>(dx) & 15u) != 0) return KATSU_OK;
+    if (!dx_takes(ctx, g, dx, n, c, h, wd, k)) return KATSU_OK;
     StemDxDims d;
     d.n = (int)n; d.k = (int)k; d.h = (int)h; d.w = (int)wd;
     d.tiles_x = (int)katsu_div_up(wd, DX_TW);
     d.tiles_y = (int)katsu_div_up(h, DX_TH);
-    if (n * size_t(d.tiles_x) * d.tiles_y > 0x3fffffffu / 8) return KATSU_OK;  // chunk counters stay in int
     d.chunks = (int)katsu_div_up(k, DX_OC);
     d.kblocks = (int)katsu_div_up(k, 32);
     d.three_pass = ctx->precision == KATSU_MODE_3XTF32 ? 1 : 0;
     d.accumulate = accumulate;
     d.status = ctx->status;
-    d.gs = c == 1 ? dx_stages<1>(d.kblocks) : c == 2 ? dx_stages<2>(d.kblocks) : dx_stages<3>(d.kblocks);
-    if (d.gs == 0) return KATSU_OK;
+    d.gs = dx_stages_for(c, d.kblocks);
+    d.gscale = gscale;
+    d.gfactor = gfactor;
     *handled = 1;
     switch (c) {
         case 1: return dx_launch<1>(ctx, w, g, dx, d);
@@ -653,22 +694,20 @@ int32_t katsu_conv_stem_tc_dx(katsu_cuda_ctx *ctx, const float *w, const float *
 }
 
 int32_t katsu_conv_stem_tc_dw(katsu_cuda_ctx *ctx, const float *x, const float *g, float *dw, size_t n, size_t c,
-                              size_t h, size_t wd, size_t k, int accumulate, int *handled) {
+                              size_t h, size_t wd, size_t k, int accumulate, const float *gscale, float gfactor,
+                              int *handled) {
     *handled = 0;
-    if (ctx->precision == KATSU_MODE_FP32) return KATSU_OK;
-    if (c < 1 || c > 3 || k < 1 || k > 64 || n == 0 || h > 32768 || wd > 32768 || wd % 4 != 0) return KATSU_OK;
-    if ((reinterpret_cast<uintptr_t>(g) & 15u) != 0 || (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return KATSU_OK;
+    if (!dw_takes(ctx, x, g, n, c, h, wd, k)) return KATSU_OK;
     StemDwDims d;
     d.n = (int)n; d.k = (int)k; d.h = (int)h; d.w = (int)wd;
     d.tiles_x = (int)katsu_div_up(wd, 32);
     d.tiles_y = (int)katsu_div_up(h, 4);
-    if (n * size_t(d.tiles_x) * d.tiles_y > 0x3fffffffu / 4) return KATSU_OK;  // K-block counters stay in int
     d.three_pass = ctx->precision == KATSU_MODE_3XTF32 ? 1 : 0;
     d.status = ctx->status;
     *handled = 1;
     switch (c) {
-        case 1: return dw_launch<1>(ctx, x, g, dw, d, accumulate);
-        case 2: return dw_launch<2>(ctx, x, g, dw, d, accumulate);
-        default: return dw_launch<3>(ctx, x, g, dw, d, accumulate);
+        case 1: return dw_launch<1>(ctx, x, g, dw, d, accumulate, gscale, gfactor);
+        case 2: return dw_launch<2>(ctx, x, g, dw, d, accumulate, gscale, gfactor);
+        default: return dw_launch<3>(ctx, x, g, dw, d, accumulate, gscale, gfactor);
     }
 }

@@ -433,13 +433,18 @@ int32_t katsu_conv_stencil_fwd(katsu_cuda_ctx *ctx, const float *x, const float 
 int32_t katsu_conv_stencil_bwd(katsu_cuda_ctx *ctx, const float *x, const float *w, const float *g,
                                float *dx, float *dw,
                                size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
-                               size_t stride, size_t pad, int accumulate, int *handled) {
+                               size_t stride, size_t pad, int accumulate, const float *gscale, float gfactor,
+                               int *handled) {
     *handled = 0;
     if (!stencil_shape(n, c, h, wd, k, r, s, stride, pad)) return KATSU_OK;
+    // only the tensor-core kernels scale the upstream gradient themselves (the caller checks)
+    const bool scaled = gscale != nullptr || gfactor != 1.f;
+    if (scaled && !katsu_conv_stem_tc_bwd_takes(ctx, x, g, dx, dw, n, c, h, wd, k)) return KATSU_OK;
     *handled = 1;
     StencilDims d = {(int)n, (int)k, (int)h, (int)wd, (int)katsu_div_up(wd, (size_t)TW), 0};
     int dx_done = 0;
-    if (dx != nullptr) KATSU_TRY(katsu_conv_stem_tc_dx(ctx, w, g, dx, n, c, h, wd, k, accumulate, &dx_done));
+    if (dx != nullptr)
+        KATSU_TRY(katsu_conv_stem_tc_dx(ctx, w, g, dx, n, c, h, wd, k, accumulate, gscale, gfactor, &dx_done));
     if (dx != nullptr && !dx_done) KATSU_TRY(katsu_stencil_dx_tma(ctx, w, g, dx, n, c, h, wd, k, accumulate, &dx_done));
     if (dx != nullptr && !dx_done) {
         switch (c) {
@@ -450,7 +455,8 @@ int32_t katsu_conv_stencil_bwd(katsu_cuda_ctx *ctx, const float *x, const float 
         }
     }
     int dw_done = 0;
-    if (dw != nullptr) KATSU_TRY(katsu_conv_stem_tc_dw(ctx, x, g, dw, n, c, h, wd, k, accumulate, &dw_done));
+    if (dw != nullptr)
+        KATSU_TRY(katsu_conv_stem_tc_dw(ctx, x, g, dw, n, c, h, wd, k, accumulate, gscale, gfactor, &dw_done));
     if (dw != nullptr && !dw_done) KATSU_TRY(katsu_stencil_dw_tma(ctx, x, g, dw, n, c, h, wd, k, accumulate, &dw_done));
     if (dw != nullptr && !dw_done) {
         switch (c) {

@@ -79,6 +79,8 @@ int kh_synchronize(void) {
 int kh_context(void **out) {
     return guarded([&] { *out = katsu::device_context(); });
 }
+void kh_set_loss_fusion(int on) { katsu::set_loss_fusion(on != 0); }
+int kh_loss_fusion(void) { return katsu::loss_fusion() ? 1 : 0; }
 
 // ---- Tensor ---------------------------------------------------------------
 int kh_tensor_new(const float *data, size_t len, const size_t *shape, size_t rank, void **out) {
@@ -130,6 +132,12 @@ void kh_tensor_op(void *h, int *kind, size_t *stride, size_t *padding) {
     *padding = op.padding;
 }
 
+void kh_tensor_op_flags(void *h, int *bias, int *relu) {
+    const katsu::Op op = T(h).op();
+    *bias = op.bias ? 1 : 0;
+    *relu = op.relu ? 1 : 0;
+}
+
 size_t kh_tensor_parent_count(void *h) { return T(h).parents().size(); }
 int kh_tensor_parent(void *h, size_t index, void **out) {
     return guarded([&] { *out = box(T(h).parents().at(index)); });
@@ -179,6 +187,9 @@ int kh_tensor_backward(void *a) {
 int kh_tensor_backward_with(void *a, const float *seed, size_t len) {
     return guarded([&] { T(a).backward_with(std::vector<float>(seed, seed + len)); });
 }
+int kh_tensor_sgd_step(void *a, float lr) {
+    return guarded([&] { T(a).sgd_step(lr); });
+}
 int kh_tensor_to_device(void *a) {
     return guarded([&] { T(a).to_device(); });
 }
@@ -202,6 +213,17 @@ int kh_conv_new_seeded(size_t in_channels, size_t out_channels, size_t kh, size_
 int kh_conv_from_weights(void *weights, size_t stride, size_t padding, void **out) {
     return guarded([&] { *out = new Conv2D(Conv2D::from_weights(T(weights), stride, padding)); });
 }
+// bias may be NULL (no bias).
+int kh_conv_from_weights_bias(void *weights, void *bias, size_t stride, size_t padding, int relu, void **out) {
+    return guarded([&] {
+        *out = new Conv2D(Conv2D::from_weights_bias(T(weights), bias ? T(bias) : Tensor(), stride, padding, relu != 0));
+    });
+}
+// *out = NULL when the layer has no bias.
+int kh_conv_bias(void *h, void **out) {
+    return guarded([&] { *out = C(h).bias().defined() ? box(C(h).bias()) : nullptr; });
+}
+int kh_conv_relu(void *h) { return C(h).relu() ? 1 : 0; }
 void kh_conv_free(void *h) { delete static_cast<Conv2D *>(h); }
 int kh_conv_weights(void *h, void **out) {
     return guarded([&] { *out = box(C(h).weights()); });

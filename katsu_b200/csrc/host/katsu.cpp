@@ -47,6 +47,7 @@ namespace {
 
 int g_ordinal = 0;
 katsu_cuda_ctx *g_ctx = nullptr;
+bool g_loss_fusion = true;
 
 void check(int32_t rc) {
     if (rc == KATSU_OK) return;
@@ -70,6 +71,9 @@ katsu_cuda_ctx *device_context() {
 void set_precision(int mode) { check(katsu_cuda_set_precision(device_context(), mode)); }
 
 void synchronize() { check(katsu_cuda_sync(device_context())); }
+
+void set_loss_fusion(bool on) { g_loss_fusion = on; }
+bool loss_fusion() { return g_loss_fusion; }
 
 // tensor.rs:127-138
 size_t element_count(const std::vector<size_t> &shape) {
@@ -96,6 +100,41 @@ DeviceBuffer::~DeviceBuffer() {
 // tensor.rs:101-107, with the data Vec replaced by {host mirror, device buffer}.
 // Values never change after construction, so either copy may be materialised
 // lazily from the other.
+// An adjoint (or a published gradient) of `numel` values that is either a dense device buffer or
+// one of the two symbolic forms the loss sub-graph sum(y * y) produces.  A symbolic form stands for
+// exactly the values the reference's node-by-node VJPs would have stored (tensor.rs:392-417):
+//   Bcast   every element is scalar[0]                       (Sum VJP into a fresh adjoint)
+//   Scaled  element i is t + t with t = fl(scalar[0] * source[i])   (both Mul edges of y * y into y's fresh adjoint)
+// `scalar` is a private one-element copy, `source` the node's own immutable values.
+struct Adjoint {
+    enum Kind { Dense, Bcast, Scaled };
+    Kind kind = Dense;
+    size_t numel = 0;
+    std::shared_ptr<DeviceBuffer> dense;   // Dense: null until first needed (then zeros)
+    std::shared_ptr<DeviceBuffer> scalar;  // Bcast, Scaled
+    std::shared_ptr<DeviceBuffer> source;  // Scaled
+
+    // Writes the values out (a no-op for an allocated dense adjoint) and returns the buffer.
+    float *to_dense() {
+        if (kind == Dense) {
+            if (!dense) dense = std::make_shared<DeviceBuffer>(numel);
+            return dense->ptr;
+        }
+        auto buffer = std::make_shared<DeviceBuffer>(numel);
+        if (numel) {
+            if (kind == Bcast)
+                check(katsu_cuda_bcast_acc(device_context(), buffer->ptr, scalar->ptr, numel));  // 0 + s
+            else
+                check(katsu_cuda_square_vjp(device_context(), buffer->ptr, source->ptr, scalar->ptr, numel, 0));
+        }
+        dense = std::move(buffer);
+        kind = Dense;
+        scalar.reset();
+        source.reset();
+        return dense->ptr;
+    }
+};
+
 struct TensorNode {
     std::vector<size_t> shape;
     size_t numel = 0;
@@ -104,7 +143,10 @@ struct TensorNode {
     mutable std::vector<float> host;
     mutable bool host_valid = false;
     mutable std::shared_ptr<DeviceBuffer> dev;  // null until uploaded / computed
-    mutable std::shared_ptr<DeviceBuffer> grad_dev;  // null == None
+    // values are parents[0] * parents[0], not computed yet (set by Tensor::mul when fusion is on)
+    mutable bool lazy_square = false;
+    mutable std::shared_ptr<DeviceBuffer> grad_dev;  // null == None (unless grad_sym holds it)
+    mutable std::shared_ptr<Adjoint> grad_sym;       // a gradient still in symbolic form
     mutable std::vector<float> grad_host;
     mutable bool grad_host_valid = false;
     mutable int borrows = 0;
@@ -112,7 +154,11 @@ struct TensorNode {
     const float *device() const {
         if (!dev) {
             auto buffer = std::make_shared<DeviceBuffer>(numel);
-            if (numel) {
+            if (lazy_square) {
+                const float *p = parents[0].device_data();
+                if (numel) check(katsu_cuda_mul(device_context(), p, p, buffer->ptr, numel));
+                lazy_square = false;
+            } else if (numel) {
                 check(katsu_cuda_h2d(device_context(), buffer->ptr, host.data(), numel));
                 check(katsu_cuda_sync(device_context()));
             }
@@ -123,11 +169,24 @@ struct TensorNode {
 
     const std::vector<float> &host_data() const {
         if (!host_valid) {
+            const float *src = device();
             host.assign(numel, 0.f);
-            if (numel) check(katsu_cuda_d2h(device_context(), host.data(), dev->ptr, numel));
+            if (numel) check(katsu_cuda_d2h(device_context(), host.data(), src, numel));
             host_valid = true;
         }
         return host;
+    }
+
+    bool has_grad() const { return grad_dev != nullptr || grad_sym != nullptr; }
+
+    // The gradient as a dense device buffer (null while it is None).
+    const std::shared_ptr<DeviceBuffer> &dense_grad() const {
+        if (grad_sym) {
+            grad_sym->to_dense();
+            grad_dev = grad_sym->dense;
+            grad_sym.reset();
+        }
+        return grad_dev;
     }
 };
 
@@ -136,16 +195,21 @@ struct TensorNode {
 // ---------------------------------------------------------------------------
 GradRef::GradRef(std::shared_ptr<TensorNode> node) : node_(std::move(node)) {
     node_->borrows += 1;
-    if (node_->grad_dev && !node_->grad_host_valid) {
-        node_->grad_host.assign(node_->numel, 0.f);
-        if (node_->numel)
-            check(katsu_cuda_d2h(device_context(), node_->grad_host.data(), node_->grad_dev->ptr, node_->numel));
-        node_->grad_host_valid = true;
+    try {
+        if (node_->has_grad() && !node_->grad_host_valid) {
+            const float *src = node_->dense_grad()->ptr;
+            node_->grad_host.assign(node_->numel, 0.f);
+            if (node_->numel) check(katsu_cuda_d2h(device_context(), node_->grad_host.data(), src, node_->numel));
+            node_->grad_host_valid = true;
+        }
+    } catch (...) {
+        node_->borrows -= 1;
+        throw;
     }
 }
 GradRef::~GradRef() { release(); }
 GradRef::GradRef(GradRef &&other) noexcept : node_(std::move(other.node_)) { other.node_.reset(); }
-bool GradRef::has_value() const { return node_ && node_->grad_dev != nullptr; }
+bool GradRef::has_value() const { return node_ && node_->has_grad(); }
 const std::vector<float> &GradRef::value() const { return node_->grad_host; }
 void GradRef::release() {
     if (node_) {
@@ -203,6 +267,7 @@ GradRef Tensor::grad() const { return GradRef(node_); }
 void Tensor::zero_grad() const {
     if (node_->borrows != 0) fail(ErrorKind::GradientBorrowed);
     node_->grad_dev.reset();
+    node_->grad_sym.reset();
     node_->grad_host.clear();
     node_->grad_host_valid = false;
 }
@@ -218,11 +283,32 @@ const Tensor &Tensor::to_host() const {
 }
 
 const float *Tensor::device_data() const { return node_->device(); }
-const float *Tensor::device_grad() const { return node_->grad_dev ? node_->grad_dev->ptr : nullptr; }
+const float *Tensor::device_grad() const { return node_->has_grad() ? node_->dense_grad()->ptr : nullptr; }
+
+Tensor Tensor::make_lazy_square(const Tensor &parent) {
+    auto node = std::make_shared<TensorNode>();
+    node->numel = parent.numel();
+    node->shape = parent.shape();
+    node->op.kind = Op::Mul;
+    node->parents = {parent, parent};
+    node->lazy_square = true;
+    return Tensor(std::move(node));
+}
+
+void Tensor::sgd_step(float lr) const {
+    if (node_->borrows != 0) fail(ErrorKind::GradientBorrowed);
+    if (!node_->has_grad()) fail(ErrorKind::Device, "sgd_step needs a gradient: run backward first");
+    const float *gradient = node_->dense_grad()->ptr;
+    float *values = const_cast<float *>(node_->device());
+    if (numel()) check(katsu_cuda_sgd_step(device_context(), values, gradient, lr, numel()));
+    node_->host_valid = false;  // the host mirror is refilled from the device on the next data()
+}
 
 // tensor.rs:226-240
 Tensor Tensor::elementwise(const Tensor &rhs, Op::Kind kind) const {
     if (shape() != rhs.shape()) fail(ErrorKind::ShapeMismatch);
+    // y * y: the values wait until somebody reads them; sum() and backward never need them stored
+    if (kind == Op::Mul && g_loss_fusion && id() == rhs.id()) return make_lazy_square(*this);
     auto out = std::make_shared<DeviceBuffer>(numel());
     const float *a = node_->device();
     const float *b = rhs.node_->device();
@@ -241,7 +327,10 @@ Tensor Tensor::mul(const Tensor &rhs) const { return elementwise(rhs, Op::Mul); 
 // tensor.rs:243-247 (tree order on the device instead of a left fold)
 Tensor Tensor::sum() const {
     auto out = std::make_shared<DeviceBuffer>(1);
-    check(katsu_cuda_sum(device_context(), node_->device(), out->ptr, numel()));
+    if (node_->lazy_square && !node_->dev)  // sum(p * p) in one pass over p, bit-identical to mul then sum
+        check(katsu_cuda_sumsq(device_context(), node_->parents[0].device_data(), out->ptr, numel()));
+    else
+        check(katsu_cuda_sum(device_context(), node_->device(), out->ptr, numel()));
     Op op;
     op.kind = Op::Sum;
     return make_node(std::move(out), {}, op, {*this});
@@ -300,16 +389,31 @@ void Tensor::backward() const {
 
 namespace {
 
-using Pending = std::unordered_map<const TensorNode *, std::shared_ptr<DeviceBuffer>>;
+// Pending adjoints of one backward pass, one per reachable node (tensor.rs:328-331).  The reference
+// zero-fills every one up front; here a dense adjoint is allocated (zero-filled) when it is first
+// needed, and the loss sub-graph's adjoints stay symbolic (see Adjoint).
+using Pending = std::unordered_map<const TensorNode *, Adjoint>;
 // Parents whose pending adjoint has received a contribution in this pass.  A pending adjoint
 // starts as zeros, so the first contribution of a convolution or matmul VJP may overwrite it
 // (0 + v == v) instead of reading it back: the read-modify-write epilogue of the strided dX
 // launches was four times slower than the plain store.
 using Touched = std::unordered_set<const TensorNode *>;
 
+bool is_square(const Tensor &node) {
+    return node.op().kind == Op::Mul && node.parents()[0].id() == node.parents()[1].id();
+}
+
+// A private one-element copy of a device scalar (the original is an adjoint that may later be
+// published as a gradient and accumulated into).
+std::shared_ptr<DeviceBuffer> copy_scalar(const float *src) {
+    auto out = std::make_shared<DeviceBuffer>(1);
+    check(katsu_cuda_d2d(device_context(), out->ptr, src, 1));
+    return out;
+}
+
 // Op::backward, tensor.rs:365-449: adds this node's contribution to the
-// pending adjoint of each parent.
-void op_backward(const Tensor &node, const float *g, Pending &pending, Touched &touched) {
+// pending adjoint of each parent.  `own` is the node's own (complete) adjoint.
+void op_backward(const Tensor &node, Adjoint &own, Pending &pending, Touched &touched) {
     katsu_cuda_ctx *ctx = device_context();
     const Op op = node.op();
     const auto &parents = node.parents();
@@ -319,18 +423,52 @@ void op_backward(const Tensor &node, const float *g, Pending &pending, Touched &
         case Op::Conv2D: {
             const Tensor &x = parents[0], &w = parents[1];
             const auto &xs = x.shape(), &ws = w.shape();
-            float *px = pending.at(x.id())->ptr, *pw = pending.at(w.id())->ptr;
+            const size_t plane = node.numel() ? node.numel() / (node.shape()[0] * node.shape()[1]) : 0;
+            // Upstream gradient of the convolution proper: a symbolic "2 * s * y" adjoint is consumed
+            // as it is (the kernels scale their outputs); bias and ReLU first take their own VJP.
+            const float *g = nullptr, *gscale = nullptr;
+            float gfactor = 1.f;
+            std::shared_ptr<DeviceBuffer> masked;
+            if (own.kind == Adjoint::Scaled && !op.relu && !op.bias && x.id() != w.id()) {
+                g = own.source->ptr;
+                gscale = own.scalar->ptr;
+                gfactor = 2.f;
+            } else {
+                g = own.to_dense();  // the bias and ReLU VJPs read the upstream gradient itself
+            }
+            if (op.bias) {
+                const Tensor &b = parents[2];
+                float *pb = pending.at(b.id()).to_dense();
+                float *dg = nullptr;
+                if (op.relu && node.numel()) {
+                    masked = std::make_shared<DeviceBuffer>(node.numel());
+                    dg = masked->ptr;
+                }
+                check(katsu_cuda_bias_relu_bwd(ctx, node.device_data(), g, dg, pb, node.shape()[0], node.shape()[1], plane,
+                                               op.relu ? 1 : 0, touched.count(b.id()) ? 1 : 0));
+                touched.insert(b.id());
+                if (dg != nullptr) g = dg;
+            } else if (op.relu && node.numel()) {
+                masked = std::make_shared<DeviceBuffer>(node.numel());
+                check(katsu_cuda_bias_relu_bwd(ctx, node.device_data(), g, masked->ptr, nullptr, node.shape()[0],
+                                               node.shape()[1], plane, 1, 0));
+                g = masked->ptr;
+            }
+            float *px = pending.at(x.id()).to_dense(), *pw = pending.at(w.id()).to_dense();
             if (x.id() != w.id()) {
                 // backward_buffers + `pending[parent] += grad` (tensor.rs:374-390)
                 const int acc_x = touched.count(x.id()) ? 1 : 0, acc_w = touched.count(w.id()) ? 1 : 0;
                 if (acc_x == acc_w) {
-                    check(katsu_cuda_conv2d_bwd(ctx, x.device_data(), w.device_data(), g, px, pw, xs[0], xs[1], xs[2],
-                                                xs[3], ws[0], ws[2], ws[3], op.stride, op.padding, acc_x));
+                    check(katsu_cuda_conv2d_bwd_scaled(ctx, x.device_data(), w.device_data(), g, gscale, gfactor, px, pw,
+                                                       xs[0], xs[1], xs[2], xs[3], ws[0], ws[2], ws[3], op.stride,
+                                                       op.padding, acc_x));
                 } else {
-                    check(katsu_cuda_conv2d_bwd(ctx, x.device_data(), w.device_data(), g, px, nullptr, xs[0], xs[1],
-                                                xs[2], xs[3], ws[0], ws[2], ws[3], op.stride, op.padding, acc_x));
-                    check(katsu_cuda_conv2d_bwd(ctx, x.device_data(), w.device_data(), g, nullptr, pw, xs[0], xs[1],
-                                                xs[2], xs[3], ws[0], ws[2], ws[3], op.stride, op.padding, acc_w));
+                    check(katsu_cuda_conv2d_bwd_scaled(ctx, x.device_data(), w.device_data(), g, gscale, gfactor, px,
+                                                       nullptr, xs[0], xs[1], xs[2], xs[3], ws[0], ws[2], ws[3], op.stride,
+                                                       op.padding, acc_x));
+                    check(katsu_cuda_conv2d_bwd_scaled(ctx, x.device_data(), w.device_data(), g, gscale, gfactor, nullptr,
+                                                       pw, xs[0], xs[1], xs[2], xs[3], ws[0], ws[2], ws[3], op.stride,
+                                                       op.padding, acc_w));
                 }
                 touched.insert(x.id());
                 touched.insert(w.id());
@@ -347,11 +485,28 @@ void op_backward(const Tensor &node, const float *g, Pending &pending, Touched &
             return;
         }
         case Op::Add:
-        case Op::Mul:
+        case Op::Mul: {
+            if (op.kind == Op::Mul && own.kind == Adjoint::Bcast && is_square(node)) {
+                // q = y * y under a broadcast adjoint s: both edges add fl(s * y) into y's adjoint
+                const Tensor &y = parents[0];
+                Adjoint &target = pending.at(y.id());
+                if (!touched.count(y.id())) {
+                    y.device_data();
+                    target.kind = Adjoint::Scaled;
+                    target.scalar = own.scalar;
+                    target.source = y.node()->dev;
+                    target.dense.reset();
+                } else if (node.numel()) {
+                    check(katsu_cuda_square_vjp(ctx, target.to_dense(), y.device_data(), own.scalar->ptr, node.numel(), 1));
+                }
+                touched.insert(y.id());
+                return;
+            }
+            const float *g = own.to_dense();
             // Both edges are visited even when they are the same node (tensor.rs:392-409).
             for (int side = 0; side < 2; ++side) {
                 const Tensor &parent = parents[side], &other = parents[1 - side];
-                float *target = pending.at(parent.id())->ptr;
+                float *target = pending.at(parent.id()).to_dense();
                 if (op.kind == Op::Add)
                     check(katsu_cuda_axpy_acc(ctx, target, g, node.numel()));
                 else
@@ -359,19 +514,32 @@ void op_backward(const Tensor &node, const float *g, Pending &pending, Touched &
                 touched.insert(parent.id());
             }
             return;
-        case Op::Sum:
-            check(katsu_cuda_bcast_acc(ctx, pending.at(parents[0].id())->ptr, g, parents[0].numel()));
-            touched.insert(parents[0].id());
+        }
+        case Op::Sum: {
+            const Tensor &parent = parents[0];
+            Adjoint &target = pending.at(parent.id());
+            const float *g = own.to_dense();
+            if (g_loss_fusion && is_square(parent) && !touched.count(parent.id())) {
+                // the adjoint of y * y is the broadcast of g[0]: kept as that one number
+                target.kind = Adjoint::Bcast;
+                target.scalar = copy_scalar(g);
+                target.dense.reset();
+            } else {
+                check(katsu_cuda_bcast_acc(ctx, target.to_dense(), g, parent.numel()));
+            }
+            touched.insert(parent.id());
             return;
+        }
         case Op::Reshape:
-            check(katsu_cuda_axpy_acc(ctx, pending.at(parents[0].id())->ptr, g, node.numel()));
+            check(katsu_cuda_axpy_acc(ctx, pending.at(parents[0].id()).to_dense(), own.to_dense(), node.numel()));
             touched.insert(parents[0].id());
             return;
         case Op::Matmul: {
             const Tensor &a = parents[0], &b = parents[1];
             const size_t m = a.shape()[0], k = a.shape()[1], n = b.shape()[1];
             if (node.numel() == 0 || k == 0) return;  // tensor.rs:421-423
-            float *pa = pending.at(a.id())->ptr, *pb = pending.at(b.id())->ptr;
+            const float *g = own.to_dense();
+            float *pa = pending.at(a.id()).to_dense(), *pb = pending.at(b.id()).to_dense();
             if (a.id() != b.id()) {
                 const int acc_a = touched.count(a.id()) ? 1 : 0, acc_b = touched.count(b.id()) ? 1 : 0;
                 if (acc_a == acc_b) {
@@ -399,24 +567,29 @@ void Tensor::backward_with(const std::vector<float> &seed) const {
     katsu_cuda_ctx *ctx = device_context();
     const std::vector<Tensor> order = topological_order();
     Pending pending;
-    for (const Tensor &node : order) pending.emplace(node.id(), std::make_shared<DeviceBuffer>(node.numel()));
+    for (const Tensor &node : order) pending[node.id()].numel = node.numel();
     if (numel() != 0) {
-        check(katsu_cuda_h2d(ctx, pending.at(id())->ptr, seed.data(), numel()));
+        check(katsu_cuda_h2d(ctx, pending.at(id()).to_dense(), seed.data(), numel()));
         check(katsu_cuda_sync(ctx));  // `seed` may be a temporary
     }
     Touched touched;
     touched.insert(id());  // the seed
-    for (auto it = order.rbegin(); it != order.rend(); ++it) op_backward(*it, pending.at(it->id())->ptr, pending, touched);
+    for (auto it = order.rbegin(); it != order.rend(); ++it) op_backward(*it, pending.at(it->id()), pending, touched);
     // All borrows are validated before any gradient changes (tensor.rs:341-350).
     for (const Tensor &node : order)
         if (node.node()->borrows != 0) fail(ErrorKind::GradientBorrowed);
     for (const Tensor &node : order) {
         TensorNode &n = *node.node();
-        std::shared_ptr<DeviceBuffer> gradient = std::move(pending.at(node.id()));
-        if (n.grad_dev) {
-            check(katsu_cuda_axpy_acc(ctx, n.grad_dev->ptr, gradient->ptr, n.numel));  // tensor.rs:353-356
+        Adjoint &adjoint = pending.at(node.id());
+        if (n.has_grad()) {
+            // tensor.rs:353-356: old += new, element by element
+            const float *add = adjoint.to_dense();
+            check(katsu_cuda_axpy_acc(ctx, n.dense_grad()->ptr, add, n.numel));
+        } else if (adjoint.kind == Adjoint::Dense) {
+            adjoint.to_dense();  // a node nothing contributed to still gets Some(zeros)
+            n.grad_dev = std::move(adjoint.dense);  // tensor.rs:357-359: the adjoint buffer becomes the gradient
         } else {
-            n.grad_dev = std::move(gradient);  // tensor.rs:357-359: the adjoint buffer becomes the gradient
+            n.grad_sym = std::make_shared<Adjoint>(std::move(adjoint));  // written out when somebody reads it
         }
         n.grad_host_valid = false;
     }
@@ -503,20 +676,34 @@ Conv2D Conv2D::from_weights(Tensor weights, size_t stride, size_t padding) {
     return Conv2D(std::move(weights), stride, padding, 0);
 }
 
+Conv2D Conv2D::from_weights_bias(Tensor weights, Tensor bias, size_t stride, size_t padding, bool relu) {
+    Conv2D layer = from_weights(std::move(weights), stride, padding);
+    if (bias.defined() && (bias.rank() != 1 || bias.shape()[0] != layer.out_channels()))
+        fail(ErrorKind::InvalidConv, "bias must have one value per output channel");
+    layer.bias_ = std::move(bias);
+    layer.relu_ = relu;
+    return layer;
+}
+
 // conv2d.rs:95-115
 Tensor Conv2D::forward(const Tensor &input) {
     const Geometry geometry(input, weights_, stride_, padding_);
     const std::vector<size_t> shape = geometry.output_shape();
     auto out = std::make_shared<DeviceBuffer>(element_count(shape));
     if (out->count != 0)
-        check(katsu_cuda_conv2d_fwd(device_context(), input.device_data(), weights_.device_data(), out->ptr,
-                                    geometry.batch, geometry.cin, geometry.h, geometry.w, geometry.cout, geometry.kh,
-                                    geometry.kw, stride_, padding_));
+        check(katsu_cuda_conv2d_fwd_bias_relu(device_context(), input.device_data(), weights_.device_data(),
+                                              bias_.defined() ? bias_.device_data() : nullptr, out->ptr, geometry.batch,
+                                              geometry.cin, geometry.h, geometry.w, geometry.cout, geometry.kh,
+                                              geometry.kw, stride_, padding_, relu_ ? 1 : 0));
     Op op;
     op.kind = Op::Conv2D;
     op.stride = stride_;
     op.padding = padding_;
-    Tensor output = Tensor::make_node(std::move(out), shape, op, {input, weights_});
+    op.bias = bias_.defined();
+    op.relu = relu_;
+    std::vector<Tensor> parents = {input, weights_};
+    if (bias_.defined()) parents.push_back(bias_);
+    Tensor output = Tensor::make_node(std::move(out), shape, op, std::move(parents));
     last_forward_ = std::make_pair(input, output);  // only reached on success
     return output;
 }
@@ -533,8 +720,16 @@ std::pair<Tensor, Tensor> Conv2D::backward(const Tensor &grad_output) const {
     if (grad_output.numel() != expected) fail(ErrorKind::DataLength, "", expected, grad_output.numel());
     auto dx = std::make_shared<DeviceBuffer>(input.numel());
     auto dw = std::make_shared<DeviceBuffer>(weights_.numel());
+    const float *g = grad_output.device_data();
+    std::shared_ptr<DeviceBuffer> masked;
+    if (relu_ && expected != 0) {  // addition: the upstream gradient passes where the activation did
+        masked = std::make_shared<DeviceBuffer>(expected);
+        check(katsu_cuda_bias_relu_bwd(device_context(), output.device_data(), g, masked->ptr, nullptr, geometry.batch,
+                                       geometry.cout, geometry.oh * geometry.ow, 1, 0));
+        g = masked->ptr;
+    }
     check(katsu_cuda_conv2d_bwd(device_context(), input.device_data(), weights_.device_data(),
-                                grad_output.device_data(), dx->ptr, dw->ptr, geometry.batch, geometry.cin, geometry.h,
+                                g, dx->ptr, dw->ptr, geometry.batch, geometry.cin, geometry.h,
                                 geometry.w, geometry.cout, geometry.kh, geometry.kw, stride_, padding_, 0));
     return {Tensor::make_node(std::move(dx), input.shape(), Op{}, {}),
             Tensor::make_node(std::move(dw), weights_.shape(), Op{}, {})};

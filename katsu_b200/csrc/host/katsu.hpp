@@ -57,7 +57,12 @@ struct Op {
     enum Kind : int { Leaf = 0, Add, Mul, Matmul, Conv2D, Sum, Reshape };
     Kind kind = Leaf;
     size_t stride = 0, padding = 0;  // Conv2D only
-    bool operator==(const Op &o) const { return kind == o.kind && stride == o.stride && padding == o.padding; }
+    // Conv2D only, additions (docs/roadmap.md:18-26 names bias and ReLU as the next layer features):
+    // the node's third parent is a bias of one value per output channel; the output went through max(., 0).
+    bool bias = false, relu = false;
+    bool operator==(const Op &o) const {
+        return kind == o.kind && stride == o.stride && padding == o.padding && bias == o.bias && relu == o.relu;
+    }
 };
 
 // Selects the device ordinal used by every tensor created afterwards in this
@@ -69,6 +74,14 @@ katsu_cuda_ctx *device_context();
 void set_precision(int mode);
 // Blocks until all queued device work is done.
 void synchronize();
+// Loss-graph fusion (default on).  When on, y.mul(&y) does not compute its values until somebody asks
+// for them, sum() of such a node reads y once, and backward carries the adjoints of that sub-graph
+// in symbolic form (a broadcast scalar for y*y, "2 * scalar * y" for y) that a convolution consumes
+// directly and that is written out only if the gradient is read.  Values and gradients are the
+// ones the reference's node-by-node evaluation gives (tensor.rs:226-247, 392-417); off evaluates
+// node by node.
+void set_loss_fusion(bool on);
+bool loss_fusion();
 
 size_t element_count(const std::vector<size_t> &shape);  // tensor.rs:127-138
 
@@ -128,6 +141,10 @@ class Tensor {
 
     void backward() const;                                 // tensor.rs:309-314
     void backward_with(const std::vector<float> &seed) const;  // tensor.rs:320-362
+    // Addition (docs/roadmap.md:21-22): data -= lr * grad in place on the device, the one operation
+    // that changes a tensor's values after construction.  Without a gradient (no backward yet, or
+    // zero_grad since) it fails with a Device error and changes nothing.
+    void sgd_step(float lr) const;
 
     // Explicit transfers of the device storage variant.
     const Tensor &to_device() const;  // uploads now instead of at first use
@@ -142,6 +159,8 @@ class Tensor {
 
     static Tensor make_node(std::shared_ptr<DeviceBuffer> data, std::vector<size_t> shape, Op op,
                             std::vector<Tensor> parents);  // Tensor::node, tensor.rs:182-190
+    // A node whose values are p * p of its (single, repeated) parent p and are computed on first use.
+    static Tensor make_lazy_square(const Tensor &parent);
 
    private:
     explicit Tensor(std::shared_ptr<TensorNode> node) : node_(std::move(node)) {}
@@ -159,6 +178,11 @@ class Conv2D {
     static Conv2D new_seeded(size_t in_channels, size_t out_channels, std::pair<size_t, size_t> kernel_size,
                              size_t stride, size_t padding, uint64_t seed);
     static Conv2D from_weights(Tensor weights, size_t stride, size_t padding);
+    // Addition: a layer with a bias of one value per output channel (an undefined Tensor for none)
+    // and, optionally, a ReLU behind it; both run in the convolution kernel's epilogue.
+    static Conv2D from_weights_bias(Tensor weights, Tensor bias, size_t stride, size_t padding, bool relu);
+    const Tensor &bias() const { return bias_; }
+    bool relu() const { return relu_; }
 
     const Tensor &weights() const { return weights_; }
     size_t in_channels() const { return weights_.shape()[1]; }
@@ -176,6 +200,8 @@ class Conv2D {
     Conv2D(Tensor weights, size_t stride, size_t padding, int)
         : weights_(std::move(weights)), stride_(stride), padding_(padding) {}
     Tensor weights_;
+    Tensor bias_;  // undefined: no bias
+    bool relu_ = false;
     size_t stride_ = 1, padding_ = 0;
     std::optional<std::pair<Tensor, Tensor>> last_forward_;
 };

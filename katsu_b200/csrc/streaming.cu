@@ -4,6 +4,8 @@
 // All are HBM-bound: 128-bit accesses, grid sized to a multiple of the SM count.
 #include "common.cuh"
 
+int32_t katsu_sum_impl(katsu_cuda_ctx *ctx, const float *a, float *out, size_t count, bool square);
+
 namespace {
 
 enum class Ew { Add, Mul, AxpyAcc, MulAcc, BcastAcc };
@@ -13,7 +15,7 @@ __device__ __forceinline__ float ew_apply(float dst, float a, float b) {
     if (OP == Ew::Add) return a + b;
     if (OP == Ew::Mul) return a * b;
     if (OP == Ew::AxpyAcc) return dst + a;
-    if (OP == Ew::MulAcc) return dst + a * b;
+    if (OP == Ew::MulAcc) return dst + __fmul_rn(a, b);  // product rounded on its own, as the reference's `+= g * other`
     return dst + a;  // BcastAcc: a is the broadcast scalar
 }
 
@@ -93,6 +95,12 @@ __device__ __forceinline__ float warp_sum(float v) {
 // Stage 1: block b folds elements b*chunk .. (b+1)*chunk into partial[b].
 // Fixed assignment of elements to threads and a fixed tree make the result
 // independent of scheduling (bit-reproducible run to run).
+// SQUARE: every element is squared (one rounded multiply, as Tensor::mul would store it) on the way
+// in, so sum(a * a) reads a once and the product tensor is never written.
+template <bool SQUARE>
+__device__ __forceinline__ float sum_term(float v) { return SQUARE ? __fmul_rn(v, v) : v; }
+
+template <bool SQUARE>
 __global__ void __launch_bounds__(256) sum_partial_kernel(const float *__restrict__ a, size_t count,
                                                           size_t chunk, float *__restrict__ partial) {
     const size_t begin = size_t(blockIdx.x) * chunk;
@@ -105,11 +113,12 @@ __global__ void __launch_bounds__(256) sum_partial_kernel(const float *__restric
         const size_t v_begin = begin / 4, v_end = end / 4;
         for (size_t i = v_begin + threadIdx.x; i < v_end; i += blockDim.x) {
             float4 v = a4[i];
-            acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+            acc[0] += sum_term<SQUARE>(v.x); acc[1] += sum_term<SQUARE>(v.y);
+            acc[2] += sum_term<SQUARE>(v.z); acc[3] += sum_term<SQUARE>(v.w);
         }
-        for (size_t i = v_end * 4 + threadIdx.x; i < end; i += blockDim.x) acc[0] += a[i];
+        for (size_t i = v_end * 4 + threadIdx.x; i < end; i += blockDim.x) acc[0] += sum_term<SQUARE>(a[i]);
     } else {
-        for (size_t i = begin + threadIdx.x; i < end; i += blockDim.x) acc[0] += a[i];
+        for (size_t i = begin + threadIdx.x; i < end; i += blockDim.x) acc[0] += sum_term<SQUARE>(a[i]);
     }
     float v = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
     __shared__ float warp_part[8];
@@ -137,7 +146,196 @@ __global__ void __launch_bounds__(256) sum_final_kernel(const float *__restrict_
     if (threadIdx.x == 0) out[0] = (float)sh[0];
 }
 
+// dst[i] (+)= t + t with t = fl(s[0] * src[i]): the two Mul VJP edges of q = y * y (both lead to y,
+// tensor.rs:392-409) under an adjoint of q that is the broadcast scalar s[0] (the Sum VJP,
+// tensor.rs:410-417).  The reference adds g*y into y's adjoint twice; (d + t) + t is kept in that order.
+template <int VEC>
+__global__ void __launch_bounds__(256) square_vjp_kernel(float *dst, const float *__restrict__ src,
+                                                         const float *__restrict__ s, size_t count, int accumulate) {
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const float scalar = __ldg(s);
+    if (VEC == 4) {
+        const size_t nvec = count / 4;
+        float4 *d4 = reinterpret_cast<float4 *>(dst);
+        const float4 *s4 = reinterpret_cast<const float4 *>(src);
+        for (; i < nvec; i += stride) {
+            const float4 v = s4[i];
+            float4 d = accumulate ? d4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float tx = __fmul_rn(scalar, v.x), ty = __fmul_rn(scalar, v.y), tz = __fmul_rn(scalar, v.z),
+                        tw = __fmul_rn(scalar, v.w);
+            d.x = (d.x + tx) + tx; d.y = (d.y + ty) + ty; d.z = (d.z + tz) + tz; d.w = (d.w + tw) + tw;
+            d4[i] = d;
+        }
+    } else {
+        for (; i < count; i += stride) {
+            const float t = __fmul_rn(scalar, src[i]);
+            const float d = accumulate ? dst[i] : 0.f;
+            dst[i] = (d + t) + t;
+        }
+    }
+}
+
+// w[i] -= fl(lr * dw[i]): plain SGD (the multiply is rounded on its own so the step is defined
+// independently of instruction selection).
+template <int VEC>
+__global__ void __launch_bounds__(256) sgd_kernel(float *w, const float *__restrict__ dw, float lr, size_t count) {
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (VEC == 4) {
+        const size_t nvec = count / 4;
+        float4 *w4 = reinterpret_cast<float4 *>(w);
+        const float4 *g4 = reinterpret_cast<const float4 *>(dw);
+        for (; i < nvec; i += stride) {
+            float4 p = w4[i];
+            const float4 g = g4[i];
+            p.x -= __fmul_rn(lr, g.x); p.y -= __fmul_rn(lr, g.y); p.z -= __fmul_rn(lr, g.z); p.w -= __fmul_rn(lr, g.w);
+            w4[i] = p;
+        }
+    } else {
+        for (; i < count; i += stride) w[i] -= __fmul_rn(lr, dw[i]);
+    }
+}
+
+// y[n, c, :] = act(y[n, c, :] + bias[c]) in place, act = max(., 0) when relu.  One block row per
+// (n, c) plane segment; used behind the convolution kernels that have no fused epilogue.
+__global__ void __launch_bounds__(256) bias_relu_kernel(float *y, const float *__restrict__ bias, size_t planes,
+                                                        size_t plane, int channels, int relu) {
+    const size_t total = planes * plane, stride = size_t(gridDim.x) * blockDim.x;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int c = int((i / plane) % size_t(channels));
+        float v = y[i] + (bias != nullptr ? __ldg(bias + c) : 0.f);
+        if (relu) v = v > 0.f ? v : 0.f;
+        y[i] = v;
+    }
+}
+
+// Backward of act(conv + bias): dg = g where the activation passed (y_act > 0) else 0 (dg == g's
+// values when there is no ReLU), and per block the sum of dg over its slice of one channel:
+// partial[slice][c].  Slices are whole images, so the fold below adds them in image order.
+__global__ void __launch_bounds__(256) bias_relu_bwd_kernel(const float *__restrict__ y_act, const float *__restrict__ g,
+                                                            float *dg, float *__restrict__ partial, int n, int channels,
+                                                            size_t plane, int images_per_slice, int relu) {
+    const int c = blockIdx.x, slice = blockIdx.y;
+    const int n0 = slice * images_per_slice;
+    int n1 = n0 + images_per_slice;
+    if (n1 > n) n1 = n;
+    float acc = 0.f;
+    for (int img = n0; img < n1; ++img) {
+        const size_t base = (size_t(img) * channels + c) * plane;
+        for (size_t p = threadIdx.x; p < plane; p += blockDim.x) {
+            float v = g[base + p];
+            if (relu && !(y_act[base + p] > 0.f)) v = 0.f;
+            if (dg != nullptr) dg[base + p] = v;
+            acc += v;
+        }
+    }
+    acc = warp_sum(acc);
+    __shared__ float warp_part[8];
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int q = 0; q < 8; ++q) t += warp_part[q];
+        partial[size_t(slice) * channels + c] = t;
+    }
+}
+
+__global__ void __launch_bounds__(256) bias_grad_fold_kernel(const float *__restrict__ partial, float *dbias, int channels,
+                                                             int slices, int accumulate) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    float t = 0.f;
+    for (int s = 0; s < slices; ++s) t += partial[size_t(s) * channels + c];
+    dbias[c] = accumulate ? dbias[c] + t : t;
+}
+
 }  // namespace
+
+int32_t katsu_bias_relu_inplace(katsu_cuda_ctx *ctx, float *y, const float *bias, size_t n, size_t k, size_t plane,
+                                int relu) {
+    if (n * k * plane == 0 || (bias == nullptr && !relu)) return KATSU_OK;
+    size_t blocks = katsu_div_up(n * k * plane, 256);
+    const size_t max_blocks = size_t(ctx->num_sms) * 8;
+    if (blocks > max_blocks) blocks = max_blocks;
+    KATSU_LAUNCH(ctx, bias_relu_kernel, (unsigned)blocks, 256, 0, y, bias, n * k, plane, (int)k, relu);
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_sumsq(katsu_cuda_ctx *ctx, const float *a, float *out, size_t count) {
+    return katsu_sum_impl(ctx, a, out, count, true);
+}
+
+extern "C" int32_t katsu_cuda_square_vjp(katsu_cuda_ctx *ctx, float *dst, const float *src, const float *s, size_t count,
+                                         int32_t accumulate) {
+    KATSU_TRY(katsu_bind(ctx));
+    if (count == 0) return KATSU_OK;
+    KATSU_REQUIRE(dst != nullptr && src != nullptr && s != nullptr, "null buffer");
+    const bool vec_ok = aligned16(dst) && aligned16(src);
+    const size_t max_blocks = size_t(ctx->num_sms) * 8;
+    const size_t body = vec_ok ? (count / 4) * 4 : 0;
+    if (body) {
+        size_t blocks = katsu_div_up(body / 4, 256);
+        if (blocks > max_blocks) blocks = max_blocks;
+        KATSU_LAUNCH(ctx, square_vjp_kernel<4>, (unsigned)blocks, 256, 0, dst, src, s, body, accumulate);
+    }
+    if (body < count) {
+        size_t blocks = katsu_div_up(count - body, 256);
+        if (blocks > max_blocks) blocks = max_blocks;
+        KATSU_LAUNCH(ctx, square_vjp_kernel<1>, (unsigned)blocks, 256, 0, dst + body, src + body, s, count - body, accumulate);
+    }
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_sgd_step(katsu_cuda_ctx *ctx, float *w, const float *dw, float lr, size_t count) {
+    KATSU_TRY(katsu_bind(ctx));
+    if (count == 0) return KATSU_OK;
+    KATSU_REQUIRE(w != nullptr && dw != nullptr, "null buffer");
+    KATSU_REQUIRE(w != dw, "w and dw must be different buffers");
+    const bool vec_ok = aligned16(w) && aligned16(dw);
+    const size_t max_blocks = size_t(ctx->num_sms) * 8;
+    const size_t body = vec_ok ? (count / 4) * 4 : 0;
+    if (body) {
+        size_t blocks = katsu_div_up(body / 4, 256);
+        if (blocks > max_blocks) blocks = max_blocks;
+        KATSU_LAUNCH(ctx, sgd_kernel<4>, (unsigned)blocks, 256, 0, w, dw, lr, body);
+    }
+    if (body < count) {
+        size_t blocks = katsu_div_up(count - body, 256);
+        if (blocks > max_blocks) blocks = max_blocks;
+        KATSU_LAUNCH(ctx, sgd_kernel<1>, (unsigned)blocks, 256, 0, w + body, dw + body, lr, count - body);
+    }
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_bias_relu_bwd(katsu_cuda_ctx *ctx, const float *y_act, const float *g, float *dg,
+                                            float *dbias, size_t n, size_t k, size_t plane, int32_t relu,
+                                            int32_t accumulate_bias) {
+    KATSU_TRY(katsu_bind(ctx));
+    KATSU_REQUIRE(k >= 1 && k <= 65535 && n <= 0x7fffffff, "channel or batch count out of range");
+    if (n * plane == 0) {
+        if (dbias != nullptr && !accumulate_bias) KATSU_CUDA_TRY(cudaMemsetAsync(dbias, 0, k * sizeof(float), ctx->stream));
+        return KATSU_OK;
+    }
+    KATSU_REQUIRE(g != nullptr, "null upstream gradient");
+    KATSU_REQUIRE(!relu || y_act != nullptr, "the ReLU mask needs the activated output");
+    KATSU_REQUIRE(dg != nullptr || dbias != nullptr, "nothing to compute");
+    // slices of whole images: enough blocks to fill the GPU, folded in image order afterwards
+    size_t slices = katsu_div_up(size_t(ctx->num_sms) * 4, k);
+    if (slices > n) slices = n;
+    if (slices > 65535) slices = 65535;
+    const size_t per_slice = katsu_div_up(n, slices);
+    slices = katsu_div_up(n, per_slice);
+    float *partial = nullptr;
+    KATSU_TRY(katsu_scratch(ctx, slices * k, &partial));
+    dim3 grid((unsigned)k, (unsigned)slices);
+    KATSU_LAUNCH(ctx, bias_relu_bwd_kernel, grid, 256, 0, y_act, g, dg, partial, (int)n, (int)k, plane, (int)per_slice,
+                 relu);
+    if (dbias != nullptr)
+        KATSU_LAUNCH(ctx, bias_grad_fold_kernel, (unsigned)katsu_div_up(k, 256), 256, 0, partial, dbias, (int)k,
+                     (int)slices, accumulate_bias);
+    return KATSU_OK;
+}
 
 extern "C" int32_t katsu_cuda_add(katsu_cuda_ctx *ctx, const float *a, const float *b, float *out, size_t count) {
     return ew_launch<Ew::Add>(ctx, out, a, b, count);
@@ -160,7 +358,7 @@ extern "C" int32_t katsu_cuda_bcast_acc(katsu_cuda_ctx *ctx, float *dst, const f
     return ew_launch<Ew::BcastAcc>(ctx, dst, g, nullptr, count);
 }
 
-extern "C" int32_t katsu_cuda_sum(katsu_cuda_ctx *ctx, const float *a, float *out, size_t count) {
+int32_t katsu_sum_impl(katsu_cuda_ctx *ctx, const float *a, float *out, size_t count, bool square) {
     KATSU_TRY(katsu_bind(ctx));
     KATSU_REQUIRE(out != nullptr, "out is null");
     if (count == 0) {
@@ -174,7 +372,14 @@ extern "C" int32_t katsu_cuda_sum(katsu_cuda_ctx *ctx, const float *a, float *ou
     parts = katsu_div_up(count, chunk);
     float *partial = nullptr;
     KATSU_TRY(katsu_scratch(ctx, parts, &partial));
-    KATSU_LAUNCH(ctx, sum_partial_kernel, (unsigned)parts, 256, 0, a, count, chunk, partial);
+    if (square)
+        KATSU_LAUNCH(ctx, sum_partial_kernel<true>, (unsigned)parts, 256, 0, a, count, chunk, partial);
+    else
+        KATSU_LAUNCH(ctx, sum_partial_kernel<false>, (unsigned)parts, 256, 0, a, count, chunk, partial);
     KATSU_LAUNCH(ctx, sum_final_kernel, 1, 256, 0, partial, (int)parts, out);
     return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_sum(katsu_cuda_ctx *ctx, const float *a, float *out, size_t count) {
+    return katsu_sum_impl(ctx, a, out, count, false);
 }

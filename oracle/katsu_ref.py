@@ -262,24 +262,29 @@ def splitmix_weights(seed, count, fan_in):
 class Op:
     """tensor.rs:85-93.  Conv2D carries (stride, padding); equality is by value."""
 
-    def __init__(self, kind, stride=None, padding=None):
-        self.kind, self.stride, self.padding = kind, stride, padding
+    def __init__(self, kind, stride=None, padding=None, bias=False, relu=False):
+        self.kind, self.stride, self.padding, self.bias, self.relu = kind, stride, padding, bias, relu
+
+    def _key(self):
+        return (self.kind, self.stride, self.padding, self.bias, self.relu)
 
     def __eq__(self, other):
-        return isinstance(other, Op) and (self.kind, self.stride, self.padding) == (
-            other.kind, other.stride, other.padding)
+        return isinstance(other, Op) and self._key() == other._key()
 
     def __hash__(self):
-        return hash((self.kind, self.stride, self.padding))
+        return hash(self._key())
 
     def __repr__(self):
         if self.kind == "Conv2D":
-            return f"Conv2D {{ stride: {self.stride}, padding: {self.padding} }}"
+            extra = (", bias" if self.bias else "") + (", relu" if self.relu else "")
+            return f"Conv2D {{ stride: {self.stride}, padding: {self.padding}{extra} }}"
         return self.kind
 
     @staticmethod
-    def Conv2D(stride, padding):
-        return Op("Conv2D", stride, padding)
+    def Conv2D(stride, padding, bias=False, relu=False):
+        """bias / relu: not in the reference (docs/roadmap.md:18-26 lists them as planned); they
+        restate the device mirror's extension with the textbook definitions."""
+        return Op("Conv2D", stride, padding, bias, relu)
 
 
 Op.Leaf, Op.Add, Op.Mul, Op.Matmul, Op.Sum, Op.Reshape = (
@@ -407,6 +412,16 @@ class Tensor:
             raise DataLength(self.numel(), count)
         return Tensor._node(self._data, shape, Op.Reshape, [self])
 
+    def sgd_step(self, lr):
+        """Not in the reference (docs/roadmap.md:21-22 plans it): data[i] -= fl(lr * grad[i]) in place,
+        the multiply rounded to f32 before the subtraction."""
+        if self._borrows:
+            raise GradientBorrowed()
+        if self._grad is None:
+            raise TensorError("sgd_step needs a gradient: run backward first")
+        step = (np.float32(lr) * self._grad).astype(np.float32)
+        self._data -= step
+
     # tensor.rs:288-306
     def _topological_order(self):
         order, visited, stack = [], set(), [(self, False)]
@@ -456,9 +471,19 @@ def _op_backward(node, g, pending):
     if op == Op.Leaf:
         return
     if op.kind == "Conv2D":
-        x, w = node._parents
+        x, w = node._parents[0], node._parents[1]
+        if op.relu:  # the gradient passes where the activation did (y > 0)
+            g = np.where(node._data > 0, g, np.float32(0)).astype(np.float32)
+        if op.bias:  # d bias[k] = sum over images, then rows, then columns, of g[:, k, :, :], f32 left to right
+            cout = node._shape[1]
+            planes = g.reshape(node._shape[0], cout, -1)
+            db = np.zeros(cout, dtype=np.float32)
+            for k in range(cout):
+                db[k] = lib().ko_sum(_p(np.ascontiguousarray(planes[:, k, :].reshape(-1))), _sz(planes.shape[0] * planes.shape[2]))
+            target = pending[id(node._parents[2])]
+            lib().ko_axpy_acc(_p(target), _p(db), _sz(target.size))
         dx, dw = backward_buffers(x, w, g, op.stride, op.padding)
-        for parent, gradient in zip(node._parents, (dx, dw)):
+        for parent, gradient in zip((x, w), (dx, dw)):
             target = pending[id(parent)]
             lib().ko_axpy_acc(_p(target), _p(gradient), _sz(target.size))
     elif op in (Op.Add, Op.Mul):
@@ -565,16 +590,27 @@ class Conv2D:
         return cls(in_channels, out_channels, kernel_size, stride, padding, seed)
 
     @classmethod
-    def from_weights(cls, weights, stride, padding):
-        """conv2d.rs:65-74"""
+    def from_weights(cls, weights, stride, padding, bias=None, relu=False):
+        """conv2d.rs:65-74.  bias (rank 1, one value per output channel) and relu are not in the
+        reference: y = max(conv(x, w) + bias[k], 0), each step rounded to f32."""
         _validate_weights(weights._shape, stride)
         _check_padding(padding)
+        if bias is not None and bias._shape != [weights._shape[0]]:
+            raise InvalidConv("bias must have one value per output channel")
         layer = cls.__new__(cls)
         layer._setup(weights, stride, padding)
+        layer._bias, layer._relu = bias, bool(relu)
         return layer
+
+    def bias(self):
+        return self._bias
+
+    def relu(self):
+        return self._relu
 
     def _setup(self, weights, stride, padding):
         self._weights, self._stride, self._padding = weights, stride, padding
+        self._bias, self._relu = None, False
         self._last_forward = None
 
     def weights(self):
@@ -604,7 +640,14 @@ class Conv2D:
                                   self._stride, self._padding)
         else:
             data = np.zeros(0, dtype=np.float32)
-        output = Tensor._node(data, shape, Op.Conv2D(self._stride, self._padding), [input, self._weights])
+        parents = [input, self._weights]
+        if self._bias is not None:
+            data = (data.reshape(shape[0], shape[1], -1) + self._bias._data.reshape(1, -1, 1)).astype(np.float32).reshape(-1)
+            parents.append(self._bias)
+        if self._relu:
+            data = np.maximum(data, np.float32(0)).astype(np.float32)
+        op = Op.Conv2D(self._stride, self._padding, self._bias is not None, self._relu)
+        output = Tensor._node(data, shape, op, parents)
         self._last_forward = (input, output)
         return output
 
@@ -615,7 +658,10 @@ class Conv2D:
         input, output = self._last_forward
         if grad_output._shape != output._shape:
             raise InvalidConv("grad_output must match the output NCHW shape")
-        dx, dw = backward_buffers(input, self._weights, grad_output._data, self._stride, self._padding)
+        grad = grad_output._data
+        if self._relu:
+            grad = np.where(output._data > 0, grad, np.float32(0)).astype(np.float32)
+        dx, dw = backward_buffers(input, self._weights, grad, self._stride, self._padding)
         return Tensor(dx, input._shape), Tensor(dw, self._weights._shape)
 
     def get_activation_map(self):
