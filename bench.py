@@ -606,7 +606,7 @@ def stem_leg(job, args):
         barrier()
     copy_min = job.reduce_over_ranks([copy_gbs["h2d"], copy_gbs["d2h"]], "min")
 
-    def e2e_step(slot):
+    def e2e_step(slot, fused=True):
         par = slot & 1
         # a lane must not overwrite a dW partial that lane 0 has not yet added (two steps back)
         for lane_ctx in lanes[1:]:
@@ -616,9 +616,16 @@ def stem_leg(job, args):
             cg = (cnt, c, h, wd, k, r, s, spec.stride, spec.pad)
             lane_ctx.h2d(b["x"], x_pin[first_img * per_img_x:(first_img + cnt) * per_img_x])
             lane_ctx.conv2d_fwd(b["x"], b["w"], b["y"], *cg)
-            lane_ctx.call("katsu_cuda_add", b["y"], b["y"], b["g"], cnt * per_img_y)
-            lane_ctx.conv2d_bwd(b["x"], b["w"], b["g"], b["dx"], 0, *cg, 0)
-            lane_ctx.conv2d_bwd(b["x"], b["w"], b["g"], 0, b["dw"][par], *cg, 1 if i >= n_lanes else 0)
+            if fused:
+                # what loss = sum(y * y) sends back is 2 * y: the backward kernels read y and scale their
+                # outputs, the gradient of y's size is never written (the graph API does the same)
+                lane_ctx.call("katsu_cuda_conv2d_bwd_scaled", b["x"], b["w"], b["y"], 0, 2.0, b["dx"], 0, *cg, 0)
+                lane_ctx.call("katsu_cuda_conv2d_bwd_scaled", b["x"], b["w"], b["y"], 0, 2.0, 0, b["dw"][par], *cg,
+                              1 if i >= n_lanes else 0)
+            else:
+                lane_ctx.call("katsu_cuda_add", b["y"], b["y"], b["g"], cnt * per_img_y)
+                lane_ctx.conv2d_bwd(b["x"], b["w"], b["g"], b["dx"], 0, *cg, 0)
+                lane_ctx.conv2d_bwd(b["x"], b["w"], b["g"], 0, b["dw"][par], *cg, 1 if i >= n_lanes else 0)
             lane_ctx.d2h_async(dx_pin[first_img * per_img_x:(first_img + cnt) * per_img_x], b["dx"])
         total = lane_buf[0]["dw"][par]
         for j in range(1, min(n_lanes, n_chunks)):
@@ -635,17 +642,23 @@ def stem_leg(job, args):
         lead.record(combined[par])
 
     lead.record(combined[0]), lead.record(combined[1])
-    e2e_step(e2e_steps)
-    for lane_ctx in lanes:
-        lane_ctx.sync()
-    barrier()
-    t0 = time.perf_counter()
-    for step_index in range(e2e_steps):
-        e2e_step(step_index)
-    for lane_ctx in lanes:
-        lane_ctx.sync()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    barrier()
+
+    def e2e_run(fused):
+        e2e_step(e2e_steps, fused)
+        for lane_ctx in lanes:
+            lane_ctx.sync()
+        barrier()
+        t0 = time.perf_counter()
+        for step_index in range(e2e_steps):
+            e2e_step(step_index, fused)
+        for lane_ctx in lanes:
+            lane_ctx.sync()
+        ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+        barrier()
+        return ms
+
+    e2e_unfused_ms = e2e_run(False)  # the gradient 2y written out by a separate pass, for comparison
+    e2e_ms = e2e_run(True)
     # Every step's dW reached the host; the inputs are the same every step, so the steps should
     # agree bit for bit.  The largest deviation from step 0 (relative to max |dW|) is reported as
     # e2e.dw_step_spread (0.0 = bit-identical); a gross difference is an error.
@@ -656,8 +669,8 @@ def stem_leg(job, args):
     dw_differing = sum(1 for i in range(1, e2e_steps) if not np.array_equal(dw_pin[0], dw_pin[i]))
 
     step_min, e2e_min = job.reduce_over_ranks([ms_per_step, e2e_ms], "min")
-    stats = [ms_per_step, e2e_ms, host_enqueue_ms, allreduce_ms or 0.0]
-    ms_per_step, e2e_ms, host_enqueue_max, allreduce_max = job.reduce_over_ranks(stats, "max")
+    stats = [ms_per_step, e2e_ms, host_enqueue_ms, allreduce_ms or 0.0, e2e_unfused_ms]
+    ms_per_step, e2e_ms, host_enqueue_max, allreduce_max, e2e_unfused_ms = job.reduce_over_ranks(stats, "max")
 
     line = None
     if rank == 0:
@@ -698,6 +711,8 @@ def stem_leg(job, args):
                     "ms_per_step_min_over_ranks": e2e_min,
                     "h2d_bytes_per_step": 4 * x_count, "d2h_bytes_per_step": 4 * (x_count + w_count),
                     "pipeline": f"{n_chunks} batch chunks over {n_lanes} streams, pinned host buffers, one host sync after the last step",
+                    "upstream_gradient": "2y read from y by the backward kernels (scaled outputs)",
+                    "ms_per_step_with_gradient_written_out": e2e_unfused_ms,
                     "copy_only_gbs_min_over_ranks": {"h2d": copy_min[0], "d2h": copy_min[1],
                                                      "note": "one direction at a time, all ranks at once"},
                     "host_affinity": affinity,
