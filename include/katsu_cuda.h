@@ -204,7 +204,10 @@ int32_t katsu_cuda_comm_unique_id(uint8_t out_id[KATSU_COMM_ID_BYTES]);
 int32_t katsu_cuda_comm_init(katsu_cuda_ctx *ctx, const uint8_t id[KATSU_COMM_ID_BYTES],
                              int32_t n_ranks, int32_t rank);
 int32_t katsu_cuda_comm_destroy(katsu_cuda_ctx *ctx);
-/* In-place sum over all ranks of a flat gradient bucket, on the context's stream. */
+/* In-place sum over all ranks of a flat gradient bucket, on the context's stream.  Buckets of up to
+ * 64 KiB on ranks that share a machine go through IPC-mapped mailboxes in one kernel per rank (a
+ * bounded wait for the peers: a rank that never arrives shows as KATSU_ERR_TIMEOUT at the next
+ * synchronising call); everything else is one ncclAllReduce.  Every rank receives the same bits. */
 int32_t katsu_cuda_allreduce_sum(katsu_cuda_ctx *ctx, float *buf, size_t count);
 
 /* ---- diagnostics (no counterpart in the reference) ------------------------ */
@@ -214,6 +217,12 @@ int32_t katsu_cuda_allreduce_sum(katsu_cuda_ctx *ctx, float *buf, size_t count);
  * KATSU_ERR_TIMEOUT once and the context remains usable.  Exercises the bounded-wait path of
  * the pipelined kernels without faulting or hanging the device. */
 int32_t katsu_cuda_selftest_wait_timeout(katsu_cuda_ctx *ctx, uint64_t cycles);
+/* Runs the mailbox all-reduce with `ranks` (1..16) emulated ranks on this one device: buf holds
+ * ranks * count floats (count <= 16384), rank r's bucket at r * count, and every bucket ends up
+ * holding the sum.  absent > 0 leaves that many ranks out; the others give up after `cycles` SM
+ * clocks (1e3..2e9) and the next synchronising call returns KATSU_ERR_TIMEOUT once. */
+int32_t katsu_cuda_selftest_mailbox_allreduce(katsu_cuda_ctx *ctx, float *buf, int32_t ranks, size_t count,
+                                              int32_t absent, uint64_t cycles);
 
 /* ---- timing on the context's stream ------------------------------------ */
 int32_t katsu_cuda_event_create(katsu_cuda_ctx *ctx, katsu_cuda_event **out_event);

@@ -74,6 +74,7 @@ SIGNATURES = {
     "katsu_cuda_wait_event": [_ctx, ctypes.c_void_p],
     "katsu_cuda_flush_l2": [_ctx],
     "katsu_cuda_selftest_wait_timeout": [_ctx, ctypes.c_uint64],
+    "katsu_cuda_selftest_mailbox_allreduce": [_ctx, _ptr, _i32, _sz, _i32, ctypes.c_uint64],
 }
 
 _lib = None

@@ -38,6 +38,8 @@ struct katsu_cuda_ctx {
     void *comm;
     int comm_ranks;
     int comm_rank;
+    // Mailbox all-reduce state of the communicator (collective.cu), null without a communicator.
+    void *mailboxes;
 };
 
 struct katsu_cuda_event {
