@@ -754,7 +754,7 @@ def other_workloads(job, args):
     for name in ("wide_128x256x56", "down_128x128x112_s2"):
         for mode in ("3xtf32", "tf32"):
             run(f"{name}/{mode}", lambda name=name, mode=mode: conv_leg(job, workloads.CONV[name], mode, steps, warmup))
-    run("small_cnn", lambda: small_cnn_leg(job, args, steps=max(steps, 5), warmup=warmup, sample_clocks=False))
+    run("small_cnn", lambda: small_cnn_leg(job, args, steps=max(steps, 20), warmup=warmup, sample_clocks=False))
     for size in (4096, 8192):
         for mode in ("3xtf32", "tf32"):
             run(f"matmul_{size}/{mode}", lambda size=size, mode=mode: gemm_leg(job, size, mode, steps, warmup))
