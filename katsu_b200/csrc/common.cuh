@@ -130,6 +130,11 @@ int32_t katsu_conv_direct_dw(katsu_cuda_ctx *ctx, const float *x, const float *g
 int32_t katsu_umma_gemm(katsu_cuda_ctx *ctx, const float *a, const float *b, float *c, size_t M, size_t N, size_t K,
                         bool a_mn, bool b_mn, int accumulate, int *handled);
 
+// The same on pairs of thread blocks (umma_gemm_pair.cu): 256 x 128 tiles, half the B traffic per block.
+// *handled = 0 when M is too small for that; operands already passed katsu_umma_gemm's alignment checks.
+int32_t katsu_umma_gemm_pair(katsu_cuda_ctx *ctx, const float *a, const float *b, float *c, size_t M, size_t N, size_t K,
+                             bool a_mn, bool b_mn, int accumulate, int *handled);
+
 // dW of a wide convolution through the GEMM kernel (umma_gemm.cu); maps and staging by the caller.
 struct CUtensorMap_st;
 int32_t katsu_umma_conv_dw(katsu_cuda_ctx *ctx, const CUtensorMap_st *map_g, const CUtensorMap_st *map_x,
