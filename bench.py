@@ -921,7 +921,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", default="stem_256x3x224", choices=sorted(workloads.CONV) + ["small_cnn"])
+    ap.add_argument("--workload", default="stem_256x3x224", choices=sorted(workloads.CONV) + ["small_cnn", "matmul"])
+    ap.add_argument("--size", type=int, default=4096, help="--workload matmul: m = k = n")
     ap.add_argument("--scaling", choices=["strong", "weak"], default="strong")
     ap.add_argument("--cpu-sample", type=int, default=32, help="images in the single-thread CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -940,6 +941,16 @@ def main():
             print(json.dumps({"impl": "reference", "unavailable": "the reference arm times the conv workloads only"}))
             return 0
         return run_small_cnn(args)
+    if args.workload == "matmul":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference arm times the conv workloads only"}))
+            return 0
+        job = Job(args)
+        entry = gemm_leg(job, args.size, args.precision, args.steps, args.warmup)
+        if job.rank == 0:
+            print(json.dumps(entry), flush=True)
+        job.close()
+        return 0
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)
