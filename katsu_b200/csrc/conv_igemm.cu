@@ -113,24 +113,32 @@ struct IgemmParams {
 // warp), warp 4 issues the TMA loads, warp 5 the MMAs.  Two accumulator sets alternate between
 // tiles so a tile's epilogue runs under the next tile's k-loop; a set is NACC_T rotating
 // accumulators (2 of 128 columns, or 4 of 64 / 32).
-template <int BNT>
+// SINGLE = single-pass TF32: no lo halves are loaded, a stage is A | B only, so the ring is twice as deep in
+// the same shared memory (the k-loop is bound by getting operands in, not by the pipe), and with 256 or more
+// output channels the tile is 128 x 256 (one accumulator of 256 columns per set): the pixel operand is then
+// fetched once per 256 instead of per 128 output channels.
+template <int BNT, bool SINGLE>
 struct IgemmCfg {
-    static constexpr int NACC_T = BNT == 128 ? 2 : 4;
+    static constexpr int NACC_T = BNT == 256 ? 1 : BNT == 128 ? 2 : 4;
     static constexpr int SET_COLS = NACC_T * BNT;
-    static constexpr int TMEM_COLS = 2 * SET_COLS;                 // 512, 512, 256
+    static constexpr int TMEM_COLS = 2 * SET_COLS;                 // 512, 512, 512, 256
     static constexpr int B_BYTES = BNT * BK * 4;
-    static constexpr int STAGE_BYTES = 2 * TILE_BYTES + 2 * B_BYTES;  // A hi | A lo | B hi | B lo
-    static constexpr int STAGES_T = BNT == 128 ? 3 : 4;
+    static constexpr int B_OFF = SINGLE ? TILE_BYTES : 2 * TILE_BYTES;  // A hi | (A lo) | B hi | (B lo)
+    static constexpr int STAGE_BYTES = SINGLE ? TILE_BYTES + B_BYTES : 2 * TILE_BYTES + 2 * B_BYTES;
+    static constexpr int FIT = (200 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES_T = SINGLE ? (FIT > 8 ? 8 : FIT) : (BNT == 128 ? 3 : 4);
     static constexpr size_t SMEM = size_t(STAGES_T) * STAGE_BYTES + 1024;
+    static_assert(SINGLE || BNT <= 128, "the split-precision stage of a 256-wide tile does not fit twice");
 };
 
-template <int BNT>
+template <int BNT, bool SINGLE>
 __global__ void __launch_bounds__(192, 1)
 conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_lo,
                   const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_b_lo,
                   const __grid_constant__ IgemmParams p, int m_tiles, int n_tiles) {
-    using Cfg = IgemmCfg<BNT>;
+    using Cfg = IgemmCfg<BNT, SINGLE>;
     constexpr int NACC_T = Cfg::NACC_T, STAGES_T = Cfg::STAGES_T;
+    constexpr int PARTS = SINGLE ? 1 : 2;  // hi, lo
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t full[STAGES_T], empty[STAGES_T], acc_full[2], acc_empty[2];
@@ -180,16 +188,16 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             for (int i = 0; i < kblocks; ++i) {
                 const int g = it * kblocks + i, s = g % STAGES_T;
                 if (g >= STAGES_T && !mbar_wait(&empty[s], ((g / STAGES_T) - 1) & 1, p.status, 21)) { ok = false; break; }
-                mbar_arrive_expect_tx(&full[s], (p.three_pass ? 2 : 1) * (TILE_BYTES + Cfg::B_BYTES));
+                mbar_arrive_expect_tx(&full[s], PARTS * (TILE_BYTES + Cfg::B_BYTES));
                 unsigned char *st = smem + s * Cfg::STAGE_BYTES;
                 const int t = i / kchunks, k0 = (i % kchunks) * BK;
-                for (int part = 0; part < (p.three_pass ? 2 : 1); ++part) {
+                for (int part = 0; part < PARTS; ++part) {
                     const CUtensorMap *ma = part ? &map_a_lo : &map_a;
                     const CUtensorMap *mb = part ? &map_b_lo : &map_b;
                     for (int h = 0; h < 2; ++h)
                         tma_load_4d(st + part * TILE_BYTES + h * (TILE_BYTES / 2), ma, &full[s], k0,
                                     bx[h] * p.bw * p.in_step + p.off_x[t], by[h] * p.bh * p.in_step + p.off_y[t], bn[h]);
-                    tma_load_4d(st + 2 * TILE_BYTES + part * Cfg::B_BYTES, mb, &full[s], k0, n0, p.b_tap[t], 0);
+                    tma_load_4d(st + Cfg::B_OFF + part * Cfg::B_BYTES, mb, &full[s], k0, n0, p.b_tap[t], 0);
                 }
             }
         }
@@ -214,10 +222,10 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 #pragma unroll
                     for (int j = 0; j < BK / 8; ++j) {
                         const uint64_t a_hi = smem_desc(st + j * 32, 16, 1024, kLayoutSw128);
-                        const uint64_t b_hi = smem_desc(st + 2 * TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
-                        if (p.three_pass) {
+                        const uint64_t b_hi = smem_desc(st + Cfg::B_OFF + j * 32, 16, 1024, kLayoutSw128);
+                        if (!SINGLE) {
                             const uint64_t a_lo = smem_desc(st + TILE_BYTES + j * 32, 16, 1024, kLayoutSw128);
-                            const uint64_t b_lo = smem_desc(st + 2 * TILE_BYTES + Cfg::B_BYTES + j * 32, 16, 1024, kLayoutSw128);
+                            const uint64_t b_lo = smem_desc(st + Cfg::B_OFF + Cfg::B_BYTES + j * 32, 16, 1024, kLayoutSw128);
                             mma_tf32(acc, a_lo, b_hi, idesc, !(first && j == 0));
                             mma_tf32(acc, a_hi, b_lo, idesc, true);
                             mma_tf32(acc, a_hi, b_hi, idesc, true);
@@ -750,28 +758,34 @@ DwPlan dw_plan(const katsu_cuda_ctx *ctx, const Shape &g) {
 
 // Forward / dX launch: picks the channel-tile width, builds the B maps for it and starts one
 // persistent block per SM (or per tile, if there are fewer).
-template <int BNT>
+template <int BNT, bool SINGLE>
 int32_t launch_igemm_bn(katsu_cuda_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &ma_lo, const float *b_hi,
                         const float *b_lo, size_t taps, size_t rows, size_t inner, const IgemmParams &p,
                         size_t total_blocks) {
     CUtensorMap mb, mb_lo;
     if (!taps_map(&mb, b_hi, taps, rows, inner, BNT) || !taps_map(&mb_lo, b_lo, taps, rows, inner, BNT))
         return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv weights)");
-    auto kernel = conv_igemm_kernel<BNT>;
-    KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)IgemmCfg<BNT>::SMEM));
+    auto kernel = conv_igemm_kernel<BNT, SINGLE>;
+    KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)IgemmCfg<BNT, SINGLE>::SMEM));
     const size_t m_tiles = katsu_div_up(total_blocks, 2), n_tiles = katsu_div_up(rows, (size_t)BNT);
     if (m_tiles * n_tiles > 0x7fffffffu / 64) return katsu_set_error(KATSU_ERR_UNSUPPORTED, "convolution too large for the tile counter");
     size_t grid = m_tiles * n_tiles;
     if (grid > (size_t)ctx->num_sms) grid = (size_t)ctx->num_sms;
-    KATSU_LAUNCH(ctx, kernel, (unsigned)grid, 192, IgemmCfg<BNT>::SMEM, ma, ma_lo, mb, mb_lo, p, (int)m_tiles, (int)n_tiles);
+    KATSU_LAUNCH(ctx, kernel, (unsigned)grid, 192, (IgemmCfg<BNT, SINGLE>::SMEM), ma, ma_lo, mb, mb_lo, p, (int)m_tiles, (int)n_tiles);
     return KATSU_OK;
 }
 
 int32_t launch_igemm(katsu_cuda_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &ma_lo, const float *b_hi,
                      const float *b_lo, size_t taps, size_t rows, size_t inner, const IgemmParams &p, size_t total_blocks) {
-    if (rows <= 32) return launch_igemm_bn<32>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
-    if (rows <= 64) return launch_igemm_bn<64>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
-    return launch_igemm_bn<128>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
+    if (!p.three_pass) {
+        if (rows <= 32) return launch_igemm_bn<32, true>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
+        if (rows <= 64) return launch_igemm_bn<64, true>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
+        if (rows < 256) return launch_igemm_bn<128, true>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
+        return launch_igemm_bn<256, true>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
+    }
+    if (rows <= 32) return launch_igemm_bn<32, false>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
+    if (rows <= 64) return launch_igemm_bn<64, false>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
+    return launch_igemm_bn<128, false>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
 }
 
 }  // namespace

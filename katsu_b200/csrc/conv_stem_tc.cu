@@ -101,12 +101,12 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
 
     if (tid == 0) {
         for (int s = 0; s < 3; ++s) {
-            mbar_init(&full[s], 128);
+            mbar_init(&full[s], 4);  // one arrival per builder warp
             mbar_init(&empty[s], 1);
         }
         for (int s = 0; s < 4; ++s) {
             mbar_init(&acc_full[s], 1);
-            mbar_init(&acc_empty[s], 128);
+            mbar_init(&acc_empty[s], 4);  // one arrival per epilogue warp
         }
         for (int s = 0; s < XS; ++s) {
             mbar_init(&x_full[s], 1);
@@ -175,7 +175,9 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
             if (d.three_pass) tmem_st_32x32(a_addr + 32, lo);
             tmem_st_wait();
             tc_fence_before_sync();
-            mbar_arrive(&full[s]);  // every thread, after its own tcgen05.wait::st
+            // tcgen05.wait::st is warp-wide: once it returns every lane's stores have landed, so one arrival per
+            // warp does (128 single arrivals are 128 serialised shared-memory operations per tile)
+            mbar_arrive_warp(&full[s]);
         }
     } else if (warp == TMA_WARP && lane == 0) {
         // ---- TMA loads of the x halo tiles ----
@@ -265,7 +267,7 @@ stem_fwd_tc_kernel(const float *__restrict__ w, float *__restrict__ y, const __g
                 }
                 if (alive && c0 + 64 >= d.np) {
                     tc_fence_before_sync();
-                    mbar_arrive(&acc_empty[b]);  // every thread, after its own tcgen05.wait::ld
+                    mbar_arrive_warp(&acc_empty[b]);  // the loads above waited for their data (tcgen05.wait::ld, warp-wide)
                 }
                 named_barrier(bar_id, 128);
                 const int chans = !alive ? 0 : (d.k - c0) < 64 ? (d.k - c0) : 64;

@@ -93,10 +93,10 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
             mbar_init(&g_empty[s], 8);
         }
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&a_full[s], 256);
+            mbar_init(&a_full[s], 8);    // one arrival per builder warp
             mbar_init(&a_empty[s], 2);
             mbar_init(&d_full[s], 2);
-            mbar_init(&d_empty[s], 128);
+            mbar_init(&d_empty[s], 4);   // one arrival per epilogue warp
         }
         mbar_init_fence();
     }
@@ -155,7 +155,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
                 tmem_st_32x32(a_addr + 32, v[1]);
                 tmem_st_wait();
                 tc_fence_before_sync();
-                mbar_arrive(&a_full[as]);
+                mbar_arrive_warp(&a_full[as]);  // tcgen05.wait::st above is warp-wide
             }
             if (!ok) break;
         }
@@ -246,7 +246,7 @@ stem_dx_tc_kernel(const float *__restrict__ w, float *dx, const __grid_constant_
                     for (int t = 0; t < TAPS; ++t) st_shared_f32(zp + t * DX_ZP, v[t]);
                 }
                 tc_fence_before_sync();
-                mbar_arrive(&d_empty[db]);
+                mbar_arrive_warp(&d_empty[db]);
             }
             if (tid == 0) tma_store_wait_read<0>();  // the previous tile's store has read `outs`
             named_barrier(1, 128);
@@ -390,13 +390,15 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
 
     if (tid == 0) {
         for (int s = 0; s < DW_GS; ++s) { mbar_init(&g_full[s], 1); mbar_init(&g_empty[s], 4); }
-        // one barrier pair per stage for A and B together (128 A-builder threads + 96 B-builder
-        // threads fill it, one commit frees it): every wait in the MMA warp's loop costs ~90 cycles.
-        // Every thread arrives itself, after its own tcgen05.wait::st (A) or proxy fence (B).
-        for (int s = 0; s < DW_AS; ++s) { mbar_init(&ab_full[s], 128 + 96); mbar_init(&ab_empty[s], 1); }
+        // one barrier pair per stage for A and B together (the four A-builder warps of the K-block's group
+        // + the three B-builder warps fill it, one commit frees it): every wait in the MMA warp's loop
+        // costs ~90 cycles.  A warp arrives once, after tcgen05.wait::st (A, warp-wide) or after every
+        // lane's proxy fence (B): 224 single arrivals per K-block were 224 serialised shared-memory
+        // operations in a kernel that is bound by the shared-memory pipe.
+        for (int s = 0; s < DW_AS; ++s) { mbar_init(&ab_full[s], 4 + 3); mbar_init(&ab_empty[s], 1); }
         for (int s = 0; s < DW_XS; ++s) { mbar_init(&x_full[s], 1); mbar_init(&x_empty[s], 3); }
         mbar_init(&d_full, 1);
-        mbar_init(&d_empty, 128);
+        mbar_init(&d_empty, 4);
         mbar_init_fence();
     }
     if (warp == DW_MMA_WARP) {
@@ -433,7 +435,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
                 }
             }
             tc_fence_before_sync();
-            mbar_arrive(&d_empty);
+            mbar_arrive_warp(&d_empty);
             return true;
         };
         bool ok = true;
@@ -467,7 +469,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
             tmem_st_32x32(lane_addr + DW_A_COL0 + uint32_t(as) * 32, v);
             tmem_st_wait();
             tc_fence_before_sync();
-            mbar_arrive(&ab_full[as]);
+            mbar_arrive_warp(&ab_full[as]);
         }
         if (group == 0) {
             if (ok) drain((my_kblocks - 1) / DW_DRAIN);
@@ -519,7 +521,7 @@ stem_dw_tc_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_consta
                     }
                 }
                 fence_proxy_async_smem();
-                mbar_arrive(&ab_full[bs]);
+                mbar_arrive_warp(&ab_full[bs]);
             }
             if (!ok) break;
             fence_proxy_async_smem();  // ordinary reads of the stage before its TMA refill
