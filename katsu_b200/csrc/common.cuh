@@ -140,7 +140,8 @@ struct CUtensorMap_st;
 int32_t katsu_umma_conv_dw(katsu_cuda_ctx *ctx, const CUtensorMap_st *map_g, const CUtensorMap_st *map_x,
                            const CUtensorMap_st *map_x_lo, float *partial, size_t k, size_t c, size_t taps,
                            size_t total_groups, size_t groups_x, size_t groups_per_img, size_t stride,
-                           const short *off_y, const short *off_x, size_t splits, size_t groups_per_split);
+                           const short *off_y, const short *off_x, size_t splits, size_t groups_per_split,
+                           int grouped_maps);
 
 // Wide-channel implicit-GEMM convolution on the tensor cores (conv_igemm.cu); *handled = 0
 // when the shape is outside what it takes.

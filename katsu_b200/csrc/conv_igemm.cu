@@ -305,6 +305,7 @@ struct DwParams {
     int groups_per_split;
     int stride;
     int three_pass;
+    int grouped;                // 1: the maps are 5-D (channel groups as a dimension), one load per operand tile
     int *status;
     short off_y[MAX_TAPS], off_x[MAX_TAPS];
 };
@@ -314,14 +315,31 @@ constexpr int DRAIN = NACC * 16;
 // 192 threads: warps 0-3 fold the accumulators (one TMEM lane quarter each), warp 4 feeds TMA,
 // warp 5 issues the MMAs.  The roles never share a thread, so the drain hand-shake cannot
 // wait on itself.
-template <int BNT>
+// SINGLE = single-pass TF32: no lo tiles, so a stage is g | x only and the ring is two to three times as deep
+// in the same shared memory; tiles are 256 input channels wide where the layer has them; and the whole
+// pixel range of a block accumulates in tensor memory without drains (the 2e-3 bar of that mode leaves room
+// for the tensor core's accumulation loss over ~40 000 terms), so no running sums are kept in registers.
+template <int BNT, bool SINGLE>
+struct DwCfg {
+    static constexpr int NACC_D = BNT == 256 ? 2 : NACC;
+    static constexpr int B_OFF = SINGLE ? TILE_BYTES : 2 * TILE_BYTES;
+    static constexpr int STAGE_BYTES = SINGLE ? TILE_BYTES + BNT * BK * 4 : 4 * TILE_BYTES;
+    static constexpr int FIT = (200 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES_D = SINGLE ? (FIT > 8 ? 8 : FIT) : STAGES;
+    static constexpr size_t SMEM = size_t(STAGES_D) * STAGE_BYTES + 1024;
+    static_assert(SINGLE || BNT <= 128, "256-wide tiles are for the single-pass form");
+};
+
+template <int BNT, bool SINGLE>
 __global__ void __launch_bounds__(192, 1)
 conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_g_lo,
                      const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_x_lo,
                      const __grid_constant__ DwParams p) {
+    using Cfg = DwCfg<BNT, SINGLE>;
+    constexpr int NACC_D = Cfg::NACC_D, STAGES_D = Cfg::STAGES_D, PARTS = SINGLE ? 1 : 2;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ uint64_t full[STAGES], empty[STAGES], drained, batch_done;
+    __shared__ uint64_t full[STAGES_D], empty[STAGES_D], drained, batch_done;
     __shared__ uint32_t tmem_slot;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ctiles = (p.c + BNT - 1) / BNT;
@@ -333,12 +351,12 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
     long long g_end = g_begin + p.groups_per_split;
     if (g_end > total_groups) g_end = total_groups;
     const int kblocks = g_end > g_begin ? int(g_end - g_begin) : 0;
-    const int tiles_per_stage = p.three_pass ? 4 : 2;
-    const uint32_t stage_bytes = 4 * TILE_BYTES;
-    const int batches = (kblocks + DRAIN - 1) / DRAIN;
+    constexpr uint32_t stage_bytes = Cfg::STAGE_BYTES;
+    const int drain_every = SINGLE ? (kblocks > 0 ? kblocks : 1) : DRAIN;  // single pass: one batch, no drains
+    const int batches = (kblocks + drain_every - 1) / drain_every;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < STAGES_D; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
@@ -347,7 +365,7 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
         mbar_init_fence();
     }
     if (warp == 4) {
-        tmem_alloc(&tmem_slot, NACC * BNT);
+        tmem_alloc(&tmem_slot, NACC_D * BNT);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -357,21 +375,29 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
 
     if (warp == 4 && lane == 0) {
         for (int i = 0; i < kblocks; ++i) {
-            const int s = i % STAGES;
-            if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, p.status, 31)) break;
-            mbar_arrive_expect_tx(&full[s], (p.three_pass ? 2 : 1) * (TILE_BYTES + BNT * BK * 4));
+            const int s = i % STAGES_D;
+            if (i >= STAGES_D && !mbar_wait(&empty[s], ((i / STAGES_D) - 1) & 1, p.status, 31)) break;
+            mbar_arrive_expect_tx(&full[s], PARTS * (TILE_BYTES + BNT * BK * 4));
             unsigned char *st = smem + s * stage_bytes;
             const long long gidx = g_begin + i;
             const int img = int(gidx / groups_per_img);
             const int r = int(gidx % groups_per_img);
             const int oy0 = (r / p.groups_x) * 4, ox0 = (r % p.groups_x) * 8;
-            for (int part = 0; part < (p.three_pass ? 2 : 1); ++part) {
+            for (int part = 0; part < PARTS; ++part) {
                 const CUtensorMap *mg = part ? &map_g_lo : &map_g;
                 const CUtensorMap *mx = part ? &map_x_lo : &map_x;
+                if (p.grouped) {
+                    // one instruction per operand tile: the TMA unit's per-instruction cost, not its
+                    // bandwidth, bounds a stage made of twelve 4 KiB boxes
+                    tma_load_5d(st + part * TILE_BYTES, mg, &full[s], 0, ox0, oy0, k0 / 32, img);
+                    tma_load_5d(st + Cfg::B_OFF + part * TILE_BYTES, mx, &full[s], 0, ox0 * p.stride + p.off_x[tap],
+                                oy0 * p.stride + p.off_y[tap], c0 / 32, img);
+                    continue;
+                }
                 for (int j = 0; j < BM / 32; ++j)
                     tma_load_4d(st + part * TILE_BYTES + j * 4096, mg, &full[s], k0 + 32 * j, ox0, oy0, img);
                 for (int j = 0; j < BNT / 32; ++j)
-                    tma_load_4d(st + (2 + part) * TILE_BYTES + j * 4096, mx, &full[s], c0 + 32 * j,
+                    tma_load_4d(st + Cfg::B_OFF + part * TILE_BYTES + j * 4096, mx, &full[s], c0 + 32 * j,
                                 ox0 * p.stride + p.off_x[tap], oy0 * p.stride + p.off_y[tap], img);
             }
         }
@@ -384,21 +410,21 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
             // the previous batch's accumulators must have been read out by all 128 threads
             if (b > 0 && !mbar_wait_warp(&drained, (b - 1) & 1, p.status, 33)) break;
             tc_fence_after_sync();
-            const int i_end = (b + 1) * DRAIN < kblocks ? (b + 1) * DRAIN : kblocks;
-            for (int i = b * DRAIN; i < i_end; ++i) {
-                const int s = i % STAGES;
-                if (!mbar_wait_warp_ready(&full[s], (i / STAGES) & 1, p.status, 32)) { ok = false; break; }
+            const int i_end = (b + 1) * drain_every < kblocks ? (b + 1) * drain_every : kblocks;
+            for (int i = b * drain_every; i < i_end; ++i) {
+                const int s = i % STAGES_D;
+                if (!mbar_wait_warp_ready(&full[s], (i / STAGES_D) & 1, p.status, 32)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t st = smem_u32(smem + s * stage_bytes);
-                const int li = i - b * DRAIN;
-                const uint32_t acc = tmem_base + uint32_t(li % NACC) * BNT;
-                const bool first = li < NACC;
+                const int li = i - b * drain_every;
+                const uint32_t acc = tmem_base + uint32_t(li % NACC_D) * BNT;
+                const bool first = li < NACC_D;
                 if (issue) {
 #pragma unroll
                     for (int j = 0; j < BK / 8; ++j) {
                         const uint64_t a_hi = smem_desc(st + j * 1024, 4096, 512, kLayoutSw128Base32);
-                        const uint64_t b_hi = smem_desc(st + 2 * TILE_BYTES + j * 1024, 4096, 512, kLayoutSw128Base32);
-                        if (p.three_pass) {
+                        const uint64_t b_hi = smem_desc(st + Cfg::B_OFF + j * 1024, 4096, 512, kLayoutSw128Base32);
+                        if (!SINGLE) {
                             const uint64_t a_lo = smem_desc(st + TILE_BYTES + j * 1024, 4096, 512, kLayoutSw128Base32);
                             const uint64_t b_lo = smem_desc(st + 3 * TILE_BYTES + j * 1024, 4096, 512, kLayoutSw128Base32);
                             mma_tf32(acc, a_lo, b_hi, idesc, !(first && j == 0));
@@ -418,7 +444,32 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
     }
     __syncwarp();
 
-    if (warp < 4) {
+    if constexpr (SINGLE) {
+      if (warp < 4) {
+        // single pass: one batch; the accumulators are added 32 columns at a time and go straight out
+        const int oc = k0 + warp * 32 + lane;
+        const bool alive = kblocks == 0 || mbar_wait(&batch_done, 0, p.status, 34);
+        tc_fence_after_sync();
+        const int used_acc = kblocks < NACC_D ? kblocks : NACC_D;
+        float *dst = p.partial + ((size_t(blockIdx.z) * p.taps + tap) * p.k + (oc < p.k ? oc : 0)) * p.c;
+        for (int q = 0; q < BNT / 32; ++q) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            for (int a = 0; a < used_acc && alive; ++a) {
+                float t[32];
+                tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + a * BNT + q * 32, t);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] += t[i];
+            }
+            if (oc < p.k) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (c0 + q * 32 + i < p.c) dst[c0 + q * 32 + i] = v[i];
+            }
+        }
+      }
+    } else if (warp < 4) {
     // running sums of this thread's output row (oc = k0 + 32*warp + lane), BNT columns
     float run[BNT];
 #pragma unroll
@@ -455,7 +506,7 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
     }  // epilogue warps
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 4) tmem_dealloc(tmem_base, NACC * BNT);
+    if (warp == 4) tmem_dealloc(tmem_base, NACC_D * BNT);
 }
 
 // ---- dW for narrow layers (C <= 32): all taps in one block ---------------------------------
@@ -677,6 +728,22 @@ bool nhwc_map(CUtensorMap *map, const float *base, size_t n, size_t h, size_t w,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The same array with its channel groups as a dimension of their own: 5-D {32 channels, W, H, C/32, N},
+// box {32, bw, bh, groups, 1}, so that one load brings `groups` 32-channel slabs, 4 KiB apart in shared
+// memory as the MN-major operand layout wants them.  C must be a multiple of 32.
+bool nhwc_grouped_map(CUtensorMap *map, const float *base, size_t n, size_t h, size_t w, size_t c, int bw, int bh,
+                      int step, int groups, CUtensorMapSwizzle swizzle) {
+    katsu_tensor_map_encode_fn encode = katsu_tensor_map_encoder();
+    if (encode == nullptr || (c & 31)) return false;
+    cuuint64_t dims[5] = {32, w, h, c / 32, n};
+    cuuint64_t strides[4] = {c * sizeof(float), w * c * sizeof(float), 32 * sizeof(float), h * w * c * sizeof(float)};
+    cuuint32_t box[5] = {32, cuuint32_t((bw - 1) * step + 1), cuuint32_t((bh - 1) * step + 1), cuuint32_t(groups), 1};
+    cuuint32_t estr[5] = {1, cuuint32_t(step), cuuint32_t(step), 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // [taps][rows][inner] weight staging array, box {32, box_rows, 1, 1} (4-D with a unit last dimension).
 bool taps_map(CUtensorMap *map, const float *base, size_t taps, size_t rows, size_t inner, int box_rows) {
     katsu_tensor_map_encode_fn encode = katsu_tensor_map_encoder();
@@ -728,8 +795,8 @@ DwPlan dw_plan(const katsu_cuda_ctx *ctx, const Shape &g) {
     const size_t taps = g.r * g.s;
     const size_t total_groups = g.n * katsu_div_up(g.ow, 8) * katsu_div_up(g.oh, 4);
     // channel-tile width of the c side: narrow layers get narrow MMAs and operand tiles
-    plan.bnt = g.c <= 32 ? 32 : g.c <= 64 ? 64 : 128;
     const bool three = ctx->precision == KATSU_MODE_3XTF32;
+    plan.bnt = g.c <= 32 ? 32 : g.c <= 64 ? 64 : (!three && g.c >= 256 && g.c % 32 == 0 && g.k % 32 == 0) ? 256 : 128;
     // two stages of (g hi/lo 32 KiB + x hi/lo 8 KiB per tap) must fit in shared memory: taps <= 10
     plan.all_taps = g.c <= 32 && g.k <= (size_t)BM && taps <= 10 && total_groups <= 0x7fffffffu;
     if (plan.all_taps) {
@@ -957,16 +1024,28 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr
     const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
     // wide layers: the GEMM kernel's convolution mode (g goes through tensor memory, its tiles
     // are read by builder threads and arrive as dense boxes; its lo halves are not needed)
-    const bool via_gemm = !plan.all_taps && bnt == 128;
+    // (3xTF32, or channel counts that rule out one-load tiles: single-pass TF32 has no lo halves to save,
+    // and with one load per operand tile its deep-ring kernel below is as fast or faster)
+    const bool whole_groups = (c % 32 == 0) && (k % 32 == 0);
+    const bool via_gemm = !plan.all_taps && bnt == 128 && (three || !whole_groups);
     bool ok = nhwc_map(&mg, gt, n, oh, ow, k, 8, 4, 1, via_gemm ? CU_TENSOR_MAP_SWIZZLE_NONE : sw) &&
               nhwc_map(&mg_lo, three ? gt_lo : gt, n, oh, ow, k, 8, 4, 1, sw) &&
               nhwc_map(&mx, xt, n, h, wd, c, 8, 4, (int)stride, sw) &&
               nhwc_map(&mx_lo, three ? xt_lo : xt, n, h, wd, c, 8, 4, (int)stride, sw);
     if (!ok) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv dW)");
+    p.grouped = 0;
+    if (!plan.all_taps && whole_groups) {
+        CUtensorMap ng, ng_lo, nx, nx_lo;
+        const bool grouped = nhwc_grouped_map(&ng, gt, n, oh, ow, k, 8, 4, 1, BM / 32, via_gemm ? CU_TENSOR_MAP_SWIZZLE_NONE : sw) &&
+                             nhwc_grouped_map(&ng_lo, three ? gt_lo : gt, n, oh, ow, k, 8, 4, 1, BM / 32, sw) &&
+                             nhwc_grouped_map(&nx, xt, n, h, wd, c, 8, 4, (int)stride, (int)bnt / 32, sw) &&
+                             nhwc_grouped_map(&nx_lo, three ? xt_lo : xt, n, h, wd, c, 8, 4, (int)stride, (int)bnt / 32, sw);
+        if (grouped) { mg = ng; mg_lo = ng_lo; mx = nx; mx_lo = nx_lo; p.grouped = 1; }
+    }
     if (via_gemm) {
         KATSU_TRY(katsu_umma_conv_dw(ctx, &mg, &mx, &mx_lo, p.partial, k, c, taps, n * p.groups_x * p.groups_y,
                                      (size_t)p.groups_x, size_t(p.groups_x) * p.groups_y, stride, p.off_y, p.off_x,
-                                     splits, (size_t)p.groups_per_split));
+                                     splits, (size_t)p.groups_per_split, p.grouped));
     } else
     if (plan.all_taps) {
         DwTapsParams q;
@@ -986,9 +1065,19 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr
         KATSU_LAUNCH(ctx, conv_dw_taps_kernel, (unsigned)grid, 192, smem, mg, mg_lo, mx, mx_lo, q);
     } else {
         dim3 grid((unsigned)(katsu_div_up(k, (size_t)BM) * katsu_div_up(c, bnt)), (unsigned)taps, (unsigned)splits);
-        auto kernel = bnt == 32 ? conv_dw_igemm_kernel<32> : bnt == 64 ? conv_dw_igemm_kernel<64> : conv_dw_igemm_kernel<128>;
-        KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-        KATSU_LAUNCH(ctx, kernel, grid, 192, kSmemBytes, mg, mg_lo, mx, mx_lo, p);
+        if (three) {
+            auto kernel = bnt == 32 ? conv_dw_igemm_kernel<32, false> : bnt == 64 ? conv_dw_igemm_kernel<64, false>
+                                                                                  : conv_dw_igemm_kernel<128, false>;
+            KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+            KATSU_LAUNCH(ctx, kernel, grid, 192, kSmemBytes, mg, mg_lo, mx, mx_lo, p);
+        } else {
+            auto kernel = bnt == 32 ? conv_dw_igemm_kernel<32, true> : bnt == 64 ? conv_dw_igemm_kernel<64, true>
+                          : bnt == 128 ? conv_dw_igemm_kernel<128, true> : conv_dw_igemm_kernel<256, true>;
+            const size_t smem = bnt == 32 ? DwCfg<32, true>::SMEM : bnt == 64 ? DwCfg<64, true>::SMEM
+                                : bnt == 128 ? DwCfg<128, true>::SMEM : DwCfg<256, true>::SMEM;
+            KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            KATSU_LAUNCH(ctx, kernel, grid, 192, smem, mg, mg_lo, mx, mx_lo, p);
+        }
     }
     KATSU_LAUNCH(ctx, dw_fold_kernel, (unsigned)katsu_div_up(k * c * taps, (size_t)32), 256, 0, p.partial, dw, (int)k,
                  (int)c, (int)taps, (int)splits, accumulate);

@@ -50,6 +50,10 @@ struct GemmParams {
     int accumulate;    // only used when splits == 1
     int three_pass;    // 3xTF32
     int *status;
+    // MN-major operand maps with the 32-wide column groups as a dimension of their own (3-D; 5-D in conv_dw
+    // mode): one load brings a whole operand tile.  The TMA unit's cost per instruction, not its bandwidth,
+    // is what a stage made of 4 KiB boxes pays for.
+    int a_grouped, b_grouped;
     // conv_dw = 1: the dW contraction of a convolution.  A = g and B = x are channels-innermost
     // staging arrays [N][H][W][C] (both MN-major), a k-block is one 8 x 4 group of output pixels,
     // blockIdx.z = split * taps + tap selects the filter tap whose shifted x window is B, and
@@ -144,10 +148,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const int k0 = (kb_begin + i) * BK;
             if (A_MN && p.conv_dw) {
                 const int gidx = kb_begin + i, img = gidx / p.groups_per_img, r = gidx % p.groups_per_img;
+                if (p.a_grouped) {
+                    tma_load_5d(ad, &map_a, &a_full[sa], 0, (r % p.groups_x) * 8, (r / p.groups_x) * 4, m0 / 32, img);
+                    continue;
+                }
                 for (int j = 0; j < BM / 32; ++j)
                     tma_load_4d(ad + j * 4096, &map_a, &a_full[sa], m0 + 32 * j, (r % p.groups_x) * 8, (r / p.groups_x) * 4, img);
             } else if (!A_MN) {
                 tma_load_2d(ad, &map_a, &a_full[sa], k0, m0);
+            } else if (p.a_grouped) {
+                tma_load_3d(ad, &map_a, &a_full[sa], 0, k0, m0 / 32);
             } else {
                 for (int j = 0; j < BM / 32; ++j) tma_load_2d(ad + j * 4096, &map_a, &a_full[sa], m0 + 32 * j, k0);
             }
@@ -165,10 +175,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (B_MN && p.conv_dw) {
                     const int gidx = kb_begin + i, img = gidx / p.groups_per_img, r = gidx % p.groups_per_img;
                     const int x0 = (r % p.groups_x) * 8 * p.stride + p.off_x[tap], y0 = (r / p.groups_x) * 4 * p.stride + p.off_y[tap];
+                    if (p.b_grouped) {
+                        tma_load_5d(bd + part * TILE_BYTES, mb, &b_full[sb], 0, x0, y0, n0 / 32, img);
+                        continue;
+                    }
                     for (int j = 0; j < BN / 32; ++j)
                         tma_load_4d(bd + part * TILE_BYTES + j * 4096, mb, &b_full[sb], n0 + 32 * j, x0, y0, img);
                 } else if (!B_MN) {
                     tma_load_2d(bd + part * TILE_BYTES, mb, &b_full[sb], k0, n0);
+                } else if (p.b_grouped) {
+                    tma_load_3d(bd + part * TILE_BYTES, mb, &b_full[sb], 0, k0, n0 / 32);
                 } else {
                     for (int j = 0; j < BN / 32; ++j) tma_load_2d(bd + part * TILE_BYTES + j * 4096, mb, &b_full[sb], n0 + 32 * j, k0);
                 }
@@ -323,22 +339,35 @@ bool aligned16(const void *ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u
 
 // Tensor map of one operand.  K-major: storage [rows][K] (K contiguous), box 32 x 128.
 // MN-major: storage [K][cols] (cols contiguous), box 32 x 32 with the 32-byte-atom swizzle.
-bool operand_map(CUtensorMap *map, const float *base, bool mn_major, size_t mn_extent, size_t k_extent) {
-    uint64_t dims[2], strides[2] = {1, 0};
-    uint32_t box[2];
+// When the MN extent is a multiple of 32 the MN-major map is 3-D {32, K, extent / 32} with box {32, 32, 4}:
+// the four 32-column slabs of a tile, 4 KiB apart in shared memory, arrive by one load (*grouped = 1).
+bool mn_major_map(CUtensorMap *map, const float *base, size_t mn_extent, size_t k_extent, CUtensorMapSwizzle swizzle,
+                  int *grouped) {
+    *grouped = (mn_extent & 31) == 0;
+    if (*grouped) {
+        const uint64_t dims[3] = {32, k_extent, mn_extent / 32}, strides[3] = {1, mn_extent, 32};
+        const uint32_t box[3] = {32, BK, BM / 32};
+        if (katsu_make_tensor_map(map, base, 3, dims, strides, box, swizzle)) return true;
+        *grouped = 0;
+    }
+    const uint64_t dims[2] = {mn_extent, k_extent}, strides[2] = {1, mn_extent};
+    const uint32_t box[2] = {32, BK};
+    return katsu_make_tensor_map(map, base, 2, dims, strides, box, swizzle);
+}
+
+bool operand_map(CUtensorMap *map, const float *base, bool mn_major, size_t mn_extent, size_t k_extent, int *grouped) {
+    *grouped = 0;
     if (!mn_major) {
-        dims[0] = k_extent; dims[1] = mn_extent; strides[1] = k_extent; box[0] = BK; box[1] = BM;
+        const uint64_t dims[2] = {k_extent, mn_extent}, strides[2] = {1, k_extent};
+        const uint32_t box[2] = {BK, BM};
         return katsu_make_tensor_map(map, base, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     }
-    dims[0] = mn_extent; dims[1] = k_extent; strides[1] = mn_extent; box[0] = 32; box[1] = BK;
-    return katsu_make_tensor_map(map, base, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    return mn_major_map(map, base, mn_extent, k_extent, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, grouped);
 }
 
 // MN-major A is read by the builder threads, not by the tensor core: dense 32 x 32 boxes.
-bool builder_map_mn(CUtensorMap *map, const float *base, size_t mn_extent, size_t k_extent) {
-    const uint64_t dims[2] = {mn_extent, k_extent}, strides[2] = {1, mn_extent};
-    const uint32_t box[2] = {32, BK};
-    return katsu_make_tensor_map(map, base, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+bool builder_map_mn(CUtensorMap *map, const float *base, size_t mn_extent, size_t k_extent, int *grouped) {
+    return mn_major_map(map, base, mn_extent, k_extent, CU_TENSOR_MAP_SWIZZLE_NONE, grouped);
 }
 
 template <bool A_MN, bool B_MN>
@@ -371,11 +400,14 @@ int32_t launch(katsu_cuda_ctx *ctx, const float *a, const float *b, float *c, si
     if (splits > 1) slabs = take(size_t(splits) * M * N);
 
     CUtensorMap map_a, map_b, map_b_lo;
-    bool ok = (A_MN ? builder_map_mn(&map_a, a, M, K) : operand_map(&map_a, a, false, M, K)) &&
-              operand_map(&map_b, b, B_MN, N, K) && operand_map(&map_b_lo, three_pass ? b_lo : b, B_MN, N, K);
-    if (!ok) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed for a matmul operand");
-
     GemmParams p;
+    int b_lo_grouped = 0;
+    bool ok = (A_MN ? builder_map_mn(&map_a, a, M, K, &p.a_grouped) : operand_map(&map_a, a, false, M, K, &p.a_grouped)) &&
+              operand_map(&map_b, b, B_MN, N, K, &p.b_grouped) &&
+              operand_map(&map_b_lo, three_pass ? b_lo : b, B_MN, N, K, &b_lo_grouped);
+    if (!ok || b_lo_grouped != p.b_grouped)
+        return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed for a matmul operand");
+
     p.c = splits > 1 ? slabs : c;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.kblocks_per_split = kb_per_split;
@@ -422,11 +454,13 @@ extern "C" int32_t katsu_cuda_selftest_wait_timeout(katsu_cuda_ctx *ctx, uint64_
 // dW of a wide convolution through the same kernel (see GemmParams::conv_dw).  The caller has
 // staged g and x (and x's lo halves) channels-innermost and built their tensor maps: g with
 // dense 32-channel x 8 x 4 boxes (read by the builders), x with the 32-byte-atom swizzle (read
-// by the tensor core), stepping `stride` pixels.  partial receives [splits][taps][k][c].
+// by the tensor core), stepping `stride` pixels; grouped_maps = 1 when they are the 5-D maps whose
+// fourth dimension counts 32-channel groups (box: four groups).  partial receives [splits][taps][k][c].
 int32_t katsu_umma_conv_dw(katsu_cuda_ctx *ctx, const CUtensorMap *map_g, const CUtensorMap *map_x,
                            const CUtensorMap *map_x_lo, float *partial, size_t k, size_t c, size_t taps,
                            size_t total_groups, size_t groups_x, size_t groups_per_img, size_t stride,
-                           const short *off_y, const short *off_x, size_t splits, size_t groups_per_split) {
+                           const short *off_y, const short *off_x, size_t splits, size_t groups_per_split,
+                           int grouped_maps) {
     if (taps > 49 || total_groups > 0x3ffffffu || splits * taps > 65535)
         return katsu_set_error(KATSU_ERR_UNSUPPORTED, "convolution too large for the dW contraction");
     GemmParams p;
@@ -438,6 +472,7 @@ int32_t katsu_umma_conv_dw(katsu_cuda_ctx *ctx, const CUtensorMap *map_g, const 
     p.three_pass = ctx->precision == KATSU_MODE_3XTF32 ? 1 : 0;
     p.status = ctx->status;
     p.conv_dw = 1;
+    p.a_grouped = p.b_grouped = grouped_maps;
     p.taps = (int)taps; p.groups_x = (int)groups_x; p.groups_per_img = (int)groups_per_img; p.stride = (int)stride;
     for (size_t t = 0; t < taps; ++t) { p.off_y[t] = off_y[t]; p.off_x[t] = off_x[t]; }
     const size_t smem = size_t(AS + 2 * BS) * TILE_BYTES + 1024;

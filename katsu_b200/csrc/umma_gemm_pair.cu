@@ -47,6 +47,7 @@ struct PairParams {
     int splits;
     int accumulate;    // only used when splits == 1
     int three_pass;
+    int a_grouped, b_grouped;  // MN-major maps are 3-D {32, K, extent / 32}: one load per operand tile
     int *status;
 };
 
@@ -113,6 +114,14 @@ __device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorM
     asm volatile(
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_addr), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_pair(void *smem_dst, const CUtensorMap *map, uint32_t bar_addr, int c0, int c1,
+                                                 int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_addr), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
 
@@ -187,6 +196,8 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             const int k0 = (kb_begin + i) * BK;
             if (!A_MN) {
                 tma_load_2d(ad, &map_a, &a_full[sa], k0, m0);
+            } else if (p.a_grouped) {
+                tma_load_3d(ad, &map_a, &a_full[sa], 0, k0, m0 / 32);
             } else {
                 for (int j = 0; j < BM / 32; ++j) tma_load_2d(ad + j * 4096, &map_a, &a_full[sa], m0 + 32 * j, k0);
             }
@@ -204,6 +215,8 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 const CUtensorMap *mb = part ? &map_b_lo : &map_b;
                 if (!B_MN) {
                     tma_load_2d_pair(bd + part * B_BYTES, mb, bar, k0, nb0);
+                } else if (p.b_grouped) {
+                    tma_load_3d_pair(bd + part * B_BYTES, mb, bar, 0, k0, nb0 / 32);
                 } else {
                     for (int j = 0; j < BH / 32; ++j) tma_load_2d_pair(bd + part * B_BYTES + j * 4096, mb, bar, nb0 + 32 * j, k0);
                 }
@@ -399,11 +412,21 @@ bool map_kmajor(CUtensorMap *map, const float *base, size_t rows_extent, size_t 
     return katsu_make_tensor_map(map, base, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-bool map_mnmajor(CUtensorMap *map, const float *base, size_t mn_extent, size_t k_extent, bool for_tensor_core) {
+// `slabs` 32-column slabs per tile; when the extent is a multiple of 32 they are a third dimension and one load
+// brings them all (*grouped = 1).
+bool map_mnmajor(CUtensorMap *map, const float *base, size_t mn_extent, size_t k_extent, bool for_tensor_core,
+                 uint32_t slabs, int *grouped) {
+    const CUtensorMapSwizzle swizzle = for_tensor_core ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
+    *grouped = (mn_extent & 31) == 0;
+    if (*grouped) {
+        const uint64_t dims[3] = {32, k_extent, mn_extent / 32}, strides[3] = {1, mn_extent, 32};
+        const uint32_t box[3] = {32, BK, slabs};
+        if (katsu_make_tensor_map(map, base, 3, dims, strides, box, swizzle)) return true;
+        *grouped = 0;
+    }
     const uint64_t dims[2] = {mn_extent, k_extent}, strides[2] = {1, mn_extent};
     const uint32_t box[2] = {32, BK};
-    return katsu_make_tensor_map(map, base, 2, dims, strides, box,
-                                 for_tensor_core ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_NONE);
+    return katsu_make_tensor_map(map, base, 2, dims, strides, box, swizzle);
 }
 
 template <bool A_MN, bool B_MN>
@@ -435,12 +458,16 @@ int32_t launch_pair(katsu_cuda_ctx *ctx, const float *a, const float *b, float *
 
     CUtensorMap map_a, map_b, map_b_lo;
     const float *b_lo_src = three_pass ? b_lo : b;
-    const bool ok = (A_MN ? map_mnmajor(&map_a, a, M, K, false) : map_kmajor(&map_a, a, M, K, BM)) &&
-                    (B_MN ? map_mnmajor(&map_b, b, N, K, true) : map_kmajor(&map_b, b, N, K, BH)) &&
-                    (B_MN ? map_mnmajor(&map_b_lo, b_lo_src, N, K, true) : map_kmajor(&map_b_lo, b_lo_src, N, K, BH));
-    if (!ok) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed for a matmul operand");
-
     PairParams p;
+    p.a_grouped = p.b_grouped = 0;
+    int b_lo_grouped = 0;
+    const bool ok = (A_MN ? map_mnmajor(&map_a, a, M, K, false, BM / 32, &p.a_grouped) : map_kmajor(&map_a, a, M, K, BM)) &&
+                    (B_MN ? map_mnmajor(&map_b, b, N, K, true, BH / 32, &p.b_grouped) : map_kmajor(&map_b, b, N, K, BH)) &&
+                    (B_MN ? map_mnmajor(&map_b_lo, b_lo_src, N, K, true, BH / 32, &b_lo_grouped)
+                          : map_kmajor(&map_b_lo, b_lo_src, N, K, BH));
+    if (!ok || b_lo_grouped != p.b_grouped)
+        return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed for a matmul operand");
+
     p.c = splits > 1 ? slabs : c;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.m_pairs = (int)m_pairs; p.n_tiles = (int)n_tiles;
