@@ -134,6 +134,9 @@ int32_t katsu_umma_gemm(katsu_cuda_ctx *ctx, const float *a, const float *b, flo
 // *handled = 0 when M is too small for that; operands already passed katsu_umma_gemm's alignment checks.
 int32_t katsu_umma_gemm_pair(katsu_cuda_ctx *ctx, const float *a, const float *b, float *c, size_t M, size_t N, size_t K,
                              bool a_mn, bool b_mn, int accumulate, int *handled);
+// Single-pass TF32 with 128 x 256 tiles (umma_gemm_wide.cu); *handled = 0 outside KATSU_MODE_TF32 or for small shapes.
+int32_t katsu_umma_gemm_wide(katsu_cuda_ctx *ctx, const float *a, const float *b, float *c, size_t M, size_t N, size_t K,
+                             bool a_mn, bool b_mn, int accumulate, int *handled);
 
 // dW of a wide convolution through the GEMM kernel (umma_gemm.cu); maps and staging by the caller.
 struct CUtensorMap_st;

@@ -497,6 +497,9 @@ int32_t katsu_umma_gemm(katsu_cuda_ctx *ctx, const float *a, const float *b, flo
     const size_t a_pitch = a_mn ? M : K, b_pitch = b_mn ? N : K;
     if ((a_pitch & 3) || (b_pitch & 3) || !aligned16(a) || !aligned16(b) || !aligned16(c)) return KATSU_OK;
     if (katsu_tensor_map_encoder() == nullptr) return KATSU_OK;
+    // single-pass TF32, large: 128 x 256 tiles straight from shared memory
+    KATSU_TRY(katsu_umma_gemm_wide(ctx, a, b, c, M, N, K, a_mn, b_mn, accumulate, handled));
+    if (*handled) return KATSU_OK;
     // tall enough for a 256-row tile: two thread blocks share each MMA and each loads half of B
     KATSU_TRY(katsu_umma_gemm_pair(ctx, a, b, c, M, N, K, a_mn, b_mn, accumulate, handled));
     if (*handled) return KATSU_OK;

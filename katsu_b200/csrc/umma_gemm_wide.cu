@@ -1,0 +1,248 @@
+// Single-pass TF32 GEMM with 128 x 256 tiles, both operands read by the tensor core from shared memory.
+//
+// Replaces, for KATSU_MODE_TF32 and large shapes, the loops of Tensor::matmul
+// (crates/katsu-core/src/tensor.rs:265-273) and of its VJP (tensor.rs:425-444).
+//
+// Why a kernel of its own.  A tcgen05 kind::tf32 MMA of one thread block runs at full rate only with
+// N = 256: back-to-back 128 x 128 x 8 MMAs issue every ~137 clocks, 128 x 256 x 8 ones every ~171, so the
+// 128 x 128 tiles of the split-precision kernel (umma_gemm.cu; its tensor-memory budget goes to the A stages
+// that 3xTF32 needs) cap single-pass TF32 at half of the pipe.  Single pass needs no lo halves and no A in
+// tensor memory: a stage is A (16 KiB) | B (32 KiB), four stages deep, and tensor memory holds two 256-column
+// accumulators so that a tile's epilogue runs under the next tile's k-loop.
+//
+// Persistent: one block per SM walks the tiles band by band (bands of RASTER_M tile rows, column-major
+// inside a band) so that blocks running together share operand tiles in L2.  Warps 0-3 are the epilogue
+// (TMEM lane quarter = warp), warp 4 issues the TMA loads, warp 5 the MMAs.  K is not split: the dispatcher
+// only sends shapes with at least one tile per two SMs here.
+#include <cstring>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 32, STAGES = 4, RASTER_M = 16;
+constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024;
+
+struct WideParams {
+    float *c;
+    int M, N, K;
+    int m_tiles, n_tiles;
+    int accumulate;
+    int a_grouped, b_grouped;  // MN-major maps are 3-D {32, K, extent / 32}: one load per operand tile
+    int *status;
+};
+
+__device__ __forceinline__ void tile_of(int tile, int m_tiles, int n_tiles, int *mt, int *nt) {
+    const int band_tiles = RASTER_M * n_tiles;
+    const int band = tile / band_tiles, r = tile % band_tiles;
+    const int rows = m_tiles - band * RASTER_M < RASTER_M ? m_tiles - band * RASTER_M : RASTER_M;
+    *mt = band * RASTER_M + r % rows;
+    *nt = r / rows;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const __grid_constant__ WideParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kblocks = (p.K + BK - 1) / BK;
+    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int my_tiles = (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
+        mbar_init_fence();
+    }
+    if (warp == 5) {
+        tmem_alloc(&tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 4 && lane == 0) {
+        // ---- TMA producer ----
+        bool ok = true;
+        for (int it = 0; it < my_tiles && ok; ++it) {
+            int mt, nt;
+            tile_of(blockIdx.x + it * gridDim.x, p.m_tiles, p.n_tiles, &mt, &nt);
+            const int m0 = mt * BM, n0 = nt * BN;
+            for (int i = 0; i < kblocks; ++i) {
+                const int g = it * kblocks + i, s = g % STAGES;
+                if (g >= STAGES && !mbar_wait(&empty[s], ((g / STAGES) - 1) & 1, p.status, 131)) { ok = false; break; }
+                mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+                unsigned char *ad = smem + s * STAGE_BYTES, *bd = ad + A_BYTES;
+                const int k0 = i * BK;
+                if (!A_MN) {
+                    tma_load_2d(ad, &map_a, &full[s], k0, m0);
+                } else if (p.a_grouped) {
+                    tma_load_3d(ad, &map_a, &full[s], 0, k0, m0 / 32);
+                } else {
+                    for (int j = 0; j < BM / 32; ++j) tma_load_2d(ad + j * 4096, &map_a, &full[s], m0 + 32 * j, k0);
+                }
+                if (!B_MN) {
+                    tma_load_2d(bd, &map_b, &full[s], k0, n0);
+                } else if (p.b_grouped) {
+                    tma_load_3d(bd, &map_b, &full[s], 0, k0, n0 / 32);
+                } else {
+                    for (int j = 0; j < BN / 32; ++j) tma_load_2d(bd + j * 4096, &map_b, &full[s], n0 + 32 * j, k0);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ---- MMA issue: whole warp in the loop, the elect.sync thread issues ----
+        const bool issue = elect_one();
+        const uint32_t idesc = idesc_tf32(BM, BN, A_MN, B_MN);
+        bool ok = true;
+        for (int it = 0; it < my_tiles && ok; ++it) {
+            const int b = it & 1;
+            if (it >= 2 && !mbar_wait_warp(&acc_empty[b], ((it >> 1) - 1) & 1, p.status, 134)) break;
+            tc_fence_after_sync();
+            const uint32_t acc = tmem_base + uint32_t(b) * BN;
+            for (int i = 0; i < kblocks; ++i) {
+                const int g = it * kblocks + i, s = g % STAGES;
+                if (!mbar_wait_warp_ready(&full[s], (g / STAGES) & 1, p.status, 132)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t ad = smem_u32(smem + s * STAGE_BYTES), bd = ad + A_BYTES;
+                if (issue) {
+#pragma unroll
+                    for (int j = 0; j < BK / 8; ++j) {
+                        const uint64_t a_desc = A_MN ? smem_desc(ad + j * 1024, 4096, 512, kLayoutSw128Base32)
+                                                     : smem_desc(ad + j * 32, 16, 1024, kLayoutSw128);
+                        const uint64_t b_desc = B_MN ? smem_desc(bd + j * 1024, 4096, 512, kLayoutSw128Base32)
+                                                     : smem_desc(bd + j * 32, 16, 1024, kLayoutSw128);
+                        mma_tf32(acc, a_desc, b_desc, idesc, !(i == 0 && j == 0));
+                    }
+                    mma_commit(&empty[s]);
+                    if (i == kblocks - 1) mma_commit(&acc_full[b]);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp < 4) {
+        // ---- epilogue: thread = row of the tile; 32 columns at a time, one 128-byte line per thread ----
+        const bool vec = (p.N & 3) == 0;
+        for (int it = 0; it < my_tiles; ++it) {
+            const int b = it & 1;
+            if (!mbar_wait_warp(&acc_full[b], (it >> 1) & 1, p.status, 133)) break;
+            tc_fence_after_sync();
+            int mt, nt;
+            tile_of(blockIdx.x + it * gridDim.x, p.m_tiles, p.n_tiles, &mt, &nt);
+            const int row = mt * BM + warp * 32 + lane, n0 = nt * BN;
+            float *dst_row = p.c + size_t(row < p.M ? row : 0) * p.N;
+            const uint32_t acc = tmem_base + (uint32_t(warp * 32) << 16) + uint32_t(b) * BN;
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                const bool last_group = c0 + 32 >= BN || n0 + c0 + 32 >= p.N;
+                float v[32];
+                tmem_ld_32x32(acc + c0, v);
+                if (last_group) {
+                    // everything this tile needs from the accumulator is in registers now
+                    tc_fence_before_sync();
+                    mbar_arrive_warp(&acc_empty[b]);
+                }
+                if (row < p.M) {
+                    float *dst = dst_row + n0 + c0;
+                    if (vec && n0 + c0 + 32 <= p.N) {
+                        float4 *d4 = reinterpret_cast<float4 *>(dst);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                            if (p.accumulate) {
+                                const float4 old = d4[i];
+                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                            }
+                            d4[i] = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (n0 + c0 + i < p.N) dst[i] = p.accumulate ? dst[i] + v[i] : v[i];
+                    }
+                }
+                if (last_group) break;
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tmem_base, 512);
+}
+
+bool wide_map(CUtensorMap *map, const float *base, bool mn_major, size_t mn_extent, size_t k_extent, uint32_t tile,
+              int *grouped) {
+    *grouped = 0;
+    if (!mn_major) {
+        const uint64_t dims[2] = {k_extent, mn_extent}, strides[2] = {1, k_extent};
+        const uint32_t box[2] = {BK, tile};
+        return katsu_make_tensor_map(map, base, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    }
+    if ((mn_extent & 31) == 0) {
+        const uint64_t dims[3] = {32, k_extent, mn_extent / 32}, strides[3] = {1, mn_extent, 32};
+        const uint32_t box[3] = {32, BK, tile / 32};
+        if (katsu_make_tensor_map(map, base, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) {
+            *grouped = 1;
+            return true;
+        }
+    }
+    const uint64_t dims[2] = {mn_extent, k_extent}, strides[2] = {1, mn_extent};
+    const uint32_t box[2] = {32, BK};
+    return katsu_make_tensor_map(map, base, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+}
+
+template <bool A_MN, bool B_MN>
+int32_t launch_wide(katsu_cuda_ctx *ctx, const float *a, const float *b, float *c, size_t M, size_t N, size_t K,
+                    int accumulate) {
+    WideParams p;
+    CUtensorMap map_a, map_b;
+    if (!wide_map(&map_a, a, A_MN, M, K, BM, &p.a_grouped) || !wide_map(&map_b, b, B_MN, N, K, BN, &p.b_grouped))
+        return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed for a matmul operand");
+    p.c = c;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.m_tiles = (int)katsu_div_up(M, (size_t)BM);
+    p.n_tiles = (int)katsu_div_up(N, (size_t)BN);
+    p.accumulate = accumulate;
+    p.status = ctx->status;
+    auto kernel = umma_gemm_wide_kernel<A_MN, B_MN>;
+    KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
+    size_t grid = size_t(p.m_tiles) * p.n_tiles;
+    if (grid > (size_t)ctx->num_sms) grid = (size_t)ctx->num_sms;
+    KATSU_LAUNCH(ctx, kernel, (unsigned)grid, 192, SMEM, map_a, map_b, p);
+    return KATSU_OK;
+}
+
+}  // namespace
+
+// C[M,N] (+)= A * B in single-pass TF32 with 128 x 256 tiles.  *handled = 0 unless the context is in
+// KATSU_MODE_TF32 and the shape gives at least one tile per two SMs (smaller shapes need the K split of the
+// 128 x 128 kernel to fill the GPU).  Alignment has been checked by the caller (katsu_umma_gemm).
+int32_t katsu_umma_gemm_wide(katsu_cuda_ctx *ctx, const float *a, const float *b, float *c, size_t M, size_t N,
+                             size_t K, bool a_mn, bool b_mn, int accumulate, int *handled) {
+    *handled = 0;
+    if (ctx->precision != KATSU_MODE_TF32) return KATSU_OK;
+    if (M < 128 || N < 256 || K < 32) return KATSU_OK;
+    const size_t tiles = katsu_div_up(M, (size_t)BM) * katsu_div_up(N, (size_t)BN);
+    if (tiles * 2 < (size_t)ctx->num_sms || tiles > 0x3fffffffu) return KATSU_OK;
+    if (katsu_div_up(K, (size_t)BK) * tiles > 0x7fffffffu) return KATSU_OK;  // the ring counter is an int
+    *handled = 1;
+    if (!a_mn && !b_mn) return launch_wide<false, false>(ctx, a, b, c, M, N, K, accumulate);
+    if (!a_mn && b_mn) return launch_wide<false, true>(ctx, a, b, c, M, N, K, accumulate);
+    if (a_mn && !b_mn) return launch_wide<true, false>(ctx, a, b, c, M, N, K, accumulate);
+    return launch_wide<true, true>(ctx, a, b, c, M, N, K, accumulate);
+}

@@ -4,14 +4,16 @@ import numpy as np
 import pytest
 
 from katsu_b200 import workloads
-from parity_util import REL_L2_TOL, DeviceArrays, assert_parity, rel_l2
+from parity_util import REL_L2_TOL, TF32_UNIT, DeviceArrays, assert_parity, max_abs_bound, rel_l2
 
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(2, 3, 2), (1, 1, 1), (70, 33, 65), (64, 64, 64), (129, 17, 200), (37, 2100, 10), (5, 4099, 3),
           (66, 2048, 16), (33, 4096, 1), (3, 5000, 17), (200, 300, 12),
           # tensor-core tiles: full and ragged in every dimension, long K (split-K)
-          (128, 128, 128), (256, 512, 384), (200, 260, 132), (1000, 96, 520), (64, 4100, 36), (130, 36, 4096)]
+          (128, 128, 128), (256, 512, 384), (200, 260, 132), (1000, 96, 520), (64, 4100, 36), (130, 36, 4096),
+          # 256-row tiles on pairs of thread blocks: odd pair count with a ragged last pair, ragged N, split K
+          (384, 4100, 200), (256, 8192, 128), (700, 64, 1000)]
 
 
 @pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
@@ -57,6 +59,38 @@ def test_same_buffer_for_both_gradients(ctx, oracle, size, accumulate):
     with DeviceArrays(ctx, a=a, g=g, d=start) as d:
         ctx.matmul_bwd(d["a"], d["a"], d["g"], d["d"], d["d"], size, size, size, accumulate)
         assert_parity(d.get("d"), expect, 2 * size, what=("same parent", size, accumulate))
+
+
+@pytest.mark.parametrize("shape", [(1100, 2080, 2304), (1152, 520, 2332)], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_large_single_pass_tf32(ctx, oracle, shape, accumulate):
+    """Shapes with at least one 128 x 256 tile per two SMs take the single-pass kernel that reads both operands
+    from shared memory: all four operand layouts (c: K-major x MN-major, dA: K x K, dB: MN x MN), ragged
+    edges in every dimension, and (second shape) an N that is not a whole number of 32-column groups."""
+    m, k, n = shape
+    rng = np.random.default_rng(m + k + n + accumulate)
+    a = rng.standard_normal(m * k).astype(np.float32)
+    b = rng.standard_normal(k * n).astype(np.float32)
+    g = rng.standard_normal(m * n).astype(np.float32)
+    c0 = rng.standard_normal(m * n).astype(np.float32)
+    da0 = rng.standard_normal(m * k).astype(np.float32) if accumulate else np.zeros(m * k, np.float32)
+    db0 = rng.standard_normal(k * n).astype(np.float32) if accumulate else np.zeros(k * n, np.float32)
+    c64 = oracle.matmul_f64(a, b, m, k, n)
+    da64, db64 = oracle.matmul_backward_f64(a, b, g, m, k, n)
+    ctx.set_precision(1)
+    try:
+        with DeviceArrays(ctx, a=a, b=b, g=g, c=c0, da=da0, db=db0) as d:
+            ctx.matmul_fwd(d["a"], d["b"], d["c"], m, k, n)
+            ctx.matmul_bwd(d["a"], d["b"], d["g"], d["da"], d["db"], m, k, n, accumulate)
+            c, da, db = d.get("c"), d.get("da"), d.get("db")
+    finally:
+        ctx.set_precision(0)
+    errors = (rel_l2(c, c64), rel_l2(da, da0.astype(np.float64) + da64), rel_l2(db, db0.astype(np.float64) + db64))
+    assert max(errors) <= 2e-3, errors
+    assert min(errors) > 1e-5, errors  # really one TF32 pass
+    # per-element bound with the TF32 unit roundoff
+    for got, ref, terms in ((c, c64, k), (da, da0 + da64, n), (db, db0 + db64, m)):
+        assert np.max(np.abs(got - ref)) <= max_abs_bound(ref, terms, unit=TF32_UNIT, sqrt_terms=False)
 
 
 @pytest.mark.parametrize("mode,bar", [(1, 2e-3), (2, REL_L2_TOL)], ids=["tf32", "fp32"])
