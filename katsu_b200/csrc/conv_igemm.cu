@@ -293,6 +293,182 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (warp == 5) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
+// ---- forward / dX, 3xTF32, 256 or more output channels ---------------------------------------
+// The k-loop of the split-precision kernel above is bound by shared-memory bandwidth: a stage's bytes are
+// written once by TMA and every MMA reads its A and B tiles from there, and with 128 x 128 tiles the twelve
+// MMAs of a k-block read 96 KiB for 64 KiB of fill.  A 128 x 256 tile needs 144 KiB of reads and 96 KiB of
+// fill for twice the work.  Tensor memory then holds exactly two 256-column accumulators, which take turns:
+// one receives DRAIN3 k-blocks (16 x 12 = 192 accumulations, shorter than the 216 of the rotating
+// accumulators above, so the split-precision error bar is kept) while the other is folded into f32
+// registers by eight epilogue warps (lane quarter = warp % 4, column half = warp / 4, 128 running sums per
+// thread).  Warp 8 issues the TMA loads, warp 9 the MMAs.  A k-block is 16 channels (64-byte rows, 64-byte
+// swizzle), so that four stages of 48 KiB fit: with two stages of 96 KiB a stage's fill and its MMAs cannot
+// overlap and the loop ran at 2480 clocks per 32 channels.
+constexpr int BK3 = 16;
+constexpr int DRAIN3 = 32;  // k-blocks of 16 channels
+constexpr int WIDE3_STAGES = 4;
+constexpr int WIDE3_A_BYTES = BM * BK3 * 4, WIDE3_B_BYTES = 256 * BK3 * 4;
+constexpr int WIDE3_STAGE_BYTES = 2 * WIDE3_A_BYTES + 2 * WIDE3_B_BYTES;
+constexpr size_t WIDE3_SMEM = size_t(WIDE3_STAGES) * WIDE3_STAGE_BYTES + 1024;
+constexpr uint32_t kLayoutSw64 = 4;
+
+__global__ void __launch_bounds__(320, 1)
+conv_igemm_wide3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_lo,
+                        const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_b_lo,
+                        const __grid_constant__ IgemmParams p, int m_tiles, int n_tiles) {
+    constexpr int BNT = 256, A_BYTES = WIDE3_A_BYTES, B_BYTES = WIDE3_B_BYTES, B_OFF = 2 * A_BYTES;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t full[WIDE3_STAGES], empty[WIDE3_STAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int blocks_per_img = p.blocks_x * p.blocks_y;
+    const int kchunks = (p.kc + BK3 - 1) / BK3;
+    const int kblocks = p.ntaps * kchunks;
+    const int batches = (kblocks + DRAIN3 - 1) / DRAIN3;
+    const int total_tiles = m_tiles * n_tiles;
+    const int my_tiles = (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < WIDE3_STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 8);
+        }
+        mbar_init_fence();
+    }
+    if (warp == 9) {
+        tmem_alloc(&tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 8 && lane == 0) {
+        // ---- TMA producer ----
+        bool ok = true;
+        for (int it = 0; it < my_tiles && ok; ++it) {
+            const int tile = blockIdx.x + it * gridDim.x;
+            const int mt = tile / n_tiles, n0 = (tile % n_tiles) * BNT;
+            int bn[2], by[2], bx[2];
+            for (int h = 0; h < 2; ++h) {
+                const long long gb = 2ll * mt + h;
+                bn[h] = int(gb / blocks_per_img);  // == n_img for a block past the end: TMA zero-fills it
+                const int r = int(gb % blocks_per_img);
+                by[h] = r / p.blocks_x;
+                bx[h] = r % p.blocks_x;
+            }
+            for (int i = 0; i < kblocks; ++i) {
+                const int g = it * kblocks + i, s = g % WIDE3_STAGES;
+                if (g >= WIDE3_STAGES && !mbar_wait(&empty[s], ((g / WIDE3_STAGES) - 1) & 1, p.status, 25)) { ok = false; break; }
+                mbar_arrive_expect_tx(&full[s], WIDE3_STAGE_BYTES);
+                unsigned char *st = smem + s * WIDE3_STAGE_BYTES;
+                const int t = i / kchunks, k0 = (i % kchunks) * BK3;
+                for (int part = 0; part < 2; ++part) {
+                    const CUtensorMap *ma = part ? &map_a_lo : &map_a;
+                    const CUtensorMap *mb = part ? &map_b_lo : &map_b;
+                    for (int h = 0; h < 2; ++h)
+                        tma_load_4d(st + part * A_BYTES + h * (A_BYTES / 2), ma, &full[s], k0,
+                                    bx[h] * p.bw * p.in_step + p.off_x[t], by[h] * p.bh * p.in_step + p.off_y[t], bn[h]);
+                    tma_load_4d(st + B_OFF + part * B_BYTES, mb, &full[s], k0, n0, p.b_tap[t], 0);
+                }
+            }
+        }
+    } else if (warp == 9) {
+        // ---- MMA issue: whole warp in the loop, the elect.sync thread issues ----
+        const bool issue = elect_one();
+        const uint32_t idesc = idesc_tf32(BM, BNT, false, false);
+        bool ok = true;
+        int q = 0;  // accumulator hand-overs so far (batches of all tiles)
+        for (int it = 0; it < my_tiles && ok; ++it) {
+            for (int bi = 0; bi < batches && ok; ++bi, ++q) {
+                const int b = q & 1;
+                if (q >= 2 && !mbar_wait_warp(&acc_empty[b], ((q >> 1) - 1) & 1, p.status, 26)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t acc = tmem_base + uint32_t(b) * BNT;
+                const int i_end = (bi + 1) * DRAIN3 < kblocks ? (bi + 1) * DRAIN3 : kblocks;
+                for (int i = bi * DRAIN3; i < i_end; ++i) {
+                    const int g = it * kblocks + i, s = g % WIDE3_STAGES;
+                    if (!mbar_wait_warp_ready(&full[s], (g / WIDE3_STAGES) & 1, p.status, 27)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t st = smem_u32(smem + s * WIDE3_STAGE_BYTES);
+                    const bool first = i == bi * DRAIN3;
+                    if (issue) {
+#pragma unroll
+                        for (int j = 0; j < BK3 / 8; ++j) {
+                            const uint64_t a_hi = smem_desc(st + j * 32, 16, 512, kLayoutSw64);
+                            const uint64_t b_hi = smem_desc(st + B_OFF + j * 32, 16, 512, kLayoutSw64);
+                            const uint64_t a_lo = smem_desc(st + A_BYTES + j * 32, 16, 512, kLayoutSw64);
+                            const uint64_t b_lo = smem_desc(st + B_OFF + B_BYTES + j * 32, 16, 512, kLayoutSw64);
+                            mma_tf32(acc, a_lo, b_hi, idesc, !(first && j == 0));
+                            mma_tf32(acc, a_hi, b_lo, idesc, true);
+                            mma_tf32(acc, a_hi, b_hi, idesc, true);
+                        }
+                        mma_commit(&empty[s]);
+                        if (i == i_end - 1) mma_commit(&acc_full[b]);
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+    } else if (warp < 8) {
+        // ---- epilogue: thread = pixel x column half; running sums in registers ----
+        const int quarter = warp & 3, half = warp >> 2;
+        const int r = quarter * 32 + lane;
+        const size_t plane = size_t(p.out_h) * p.out_w;
+        int q = 0;
+        bool alive = true;
+        for (int it = 0; it < my_tiles && alive; ++it) {
+            float run[128];
+#pragma unroll
+            for (int i = 0; i < 128; ++i) run[i] = 0.f;
+            for (int bi = 0; bi < batches; ++bi, ++q) {
+                const int b = q & 1;
+                if (!mbar_wait_warp(&acc_full[b], (q >> 1) & 1, p.status, 28)) { alive = false; break; }
+                tc_fence_after_sync();
+                const uint32_t acc = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(b) * BNT + uint32_t(half) * 128;
+#pragma unroll
+                for (int c0 = 0; c0 < 128; c0 += 32) {
+                    float t[32];
+                    tmem_ld_32x32(acc + c0, t);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) run[c0 + i] += t[i];
+                }
+                tc_fence_before_sync();
+                mbar_arrive_warp(&acc_empty[b]);
+            }
+            if (!alive) break;
+            const int tile = blockIdx.x + it * gridDim.x;
+            const int mt = tile / n_tiles, n0 = (tile % n_tiles) * BNT + half * 128;
+            const long long gb = 2ll * mt + (r >> 6);
+            const int img = int(gb / blocks_per_img);
+            const int rb = int(gb % blocks_per_img);
+            const int jy = (rb / p.blocks_x) * p.bh + (r & 63) / p.bw;
+            const int jx = (rb % p.blocks_x) * p.bw + (r & 63) % p.bw;
+            if (img < p.n_img && jy < p.grid_h && jx < p.grid_w) {
+                const int oy = p.out_sy * jy + p.out_oy, ox = p.out_sx * jx + p.out_ox;
+                float *dst_px = p.out + size_t(img) * p.out_c * plane + size_t(oy) * p.out_w + ox;
+#pragma unroll
+                for (int i = 0; i < 128; ++i) {
+                    const int ch = n0 + i;
+                    if (ch < p.out_c) {
+                        float *dst = dst_px + size_t(ch) * plane;
+                        *dst = p.accumulate ? *dst + run[i] : run[i];
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 9) tmem_dealloc(tmem_base, 512);
+}
+
 // ---- dW kernel ------------------------------------------------------------------------
 // One block: output tile [128 oc x 128 c] of one tap, over a range of 32-pixel groups
 // (4 rows x 8 pixels of one image).  A = G staged [pixel][oc], B = X staged
@@ -716,12 +892,12 @@ size_t padded(size_t n) { return (n + 63) / 64 * 64; }
 
 // [N][H][W][C] staging array as a 4-D tensor map, box {32 channels, bw, bh, 1}; step > 1 walks every step-th pixel.
 bool nhwc_map(CUtensorMap *map, const float *base, size_t n, size_t h, size_t w, size_t c, int bw, int bh, int step,
-              CUtensorMapSwizzle swizzle) {
+              CUtensorMapSwizzle swizzle, int box_c = 32) {
     katsu_tensor_map_encode_fn encode = katsu_tensor_map_encoder();
     if (encode == nullptr) return false;
     cuuint64_t dims[4] = {c, w, h, n};
     cuuint64_t strides[3] = {c * sizeof(float), w * c * sizeof(float), h * w * c * sizeof(float)};
-    cuuint32_t box[4] = {32, cuuint32_t((bw - 1) * step + 1), cuuint32_t((bh - 1) * step + 1), 1};
+    cuuint32_t box[4] = {cuuint32_t(box_c), cuuint32_t((bw - 1) * step + 1), cuuint32_t((bh - 1) * step + 1), 1};
     cuuint32_t estr[4] = {1, cuuint32_t(step), cuuint32_t(step), 1};
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -745,15 +921,16 @@ bool nhwc_grouped_map(CUtensorMap *map, const float *base, size_t n, size_t h, s
 }
 
 // [taps][rows][inner] weight staging array, box {32, box_rows, 1, 1} (4-D with a unit last dimension).
-bool taps_map(CUtensorMap *map, const float *base, size_t taps, size_t rows, size_t inner, int box_rows) {
+bool taps_map(CUtensorMap *map, const float *base, size_t taps, size_t rows, size_t inner, int box_rows,
+              int box_inner = 32, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
     katsu_tensor_map_encode_fn encode = katsu_tensor_map_encoder();
     if (encode == nullptr) return false;
     cuuint64_t dims[4] = {inner, rows, taps, 1};
     cuuint64_t strides[3] = {inner * sizeof(float), rows * inner * sizeof(float), taps * rows * inner * sizeof(float)};
-    cuuint32_t box[4] = {32, cuuint32_t(box_rows), 1, 1};
+    cuuint32_t box[4] = {cuuint32_t(box_inner), cuuint32_t(box_rows), 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -842,16 +1019,45 @@ int32_t launch_igemm_bn(katsu_cuda_ctx *ctx, const CUtensorMap &ma, const CUtens
     return KATSU_OK;
 }
 
+// 256-wide tiles do a third more work per unit of shared-memory traffic; they pay unless padding the
+// channel count to a multiple of 256 adds more than a fifth over padding it to a multiple of 128.
+bool wide_tiles_pay(size_t rows) {
+    return rows >= 256 && katsu_div_up(rows, (size_t)256) * 256 * 10 <= katsu_div_up(rows, (size_t)128) * 128 * 12;
+}
+
+// The staged activation operand of a forward / dX launch, for kernels that build their own maps of it.
+struct Activation {
+    const float *hi, *lo;
+    size_t n, h, w, c;
+    int step;
+};
+
 int32_t launch_igemm(katsu_cuda_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &ma_lo, const float *b_hi,
-                     const float *b_lo, size_t taps, size_t rows, size_t inner, const IgemmParams &p, size_t total_blocks) {
+                     const float *b_lo, size_t taps, size_t rows, size_t inner, const IgemmParams &p, size_t total_blocks,
+                     const Activation &act) {
     if (!p.three_pass) {
         if (rows <= 32) return launch_igemm_bn<32, true>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
         if (rows <= 64) return launch_igemm_bn<64, true>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
-        if (rows < 256) return launch_igemm_bn<128, true>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
+        if (!wide_tiles_pay(rows)) return launch_igemm_bn<128, true>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
         return launch_igemm_bn<256, true>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
     }
     if (rows <= 32) return launch_igemm_bn<32, false>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
     if (rows <= 64) return launch_igemm_bn<64, false>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
+    if (wide_tiles_pay(rows)) {
+        CUtensorMap mb, mb_lo, wa, wa_lo;
+        const CUtensorMapSwizzle sw64 = CU_TENSOR_MAP_SWIZZLE_64B;
+        if (!taps_map(&mb, b_hi, taps, rows, inner, 256, BK3, sw64) || !taps_map(&mb_lo, b_lo, taps, rows, inner, 256, BK3, sw64) ||
+            !nhwc_map(&wa, act.hi, act.n, act.h, act.w, act.c, p.bw, p.bh, act.step, sw64, BK3) ||
+            !nhwc_map(&wa_lo, act.lo, act.n, act.h, act.w, act.c, p.bw, p.bh, act.step, sw64, BK3))
+            return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (wide conv operands)");
+        KATSU_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_wide3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WIDE3_SMEM));
+        const size_t m_tiles = katsu_div_up(total_blocks, 2), n_tiles = katsu_div_up(rows, (size_t)256);
+        if (m_tiles * n_tiles > 0x7fffffffu / 64) return katsu_set_error(KATSU_ERR_UNSUPPORTED, "convolution too large for the tile counter");
+        size_t grid = m_tiles * n_tiles;
+        if (grid > (size_t)ctx->num_sms) grid = (size_t)ctx->num_sms;
+        KATSU_LAUNCH(ctx, conv_igemm_wide3_kernel, (unsigned)grid, 320, WIDE3_SMEM, wa, wa_lo, mb, mb_lo, p, (int)m_tiles, (int)n_tiles);
+        return KATSU_OK;
+    }
     return launch_igemm_bn<128, false>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
 }
 
@@ -899,7 +1105,8 @@ int32_t katsu_conv_igemm_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w
               nhwc_map(&ma_lo, three ? xt_lo : xt, n, h, wd, c, p.bw, p.bh, (int)stride, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!ok) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv forward)");
     const size_t total_blocks = n * p.blocks_x * p.blocks_y;
-    return launch_igemm(ctx, ma, ma_lo, wf, three ? wf_lo : wf, taps, k, c, p, total_blocks);
+    const Activation act = {xt, three ? xt_lo : xt, n, h, wd, c, (int)stride};
+    return launch_igemm(ctx, ma, ma_lo, wf, three ? wf_lo : wf, taps, k, c, p, total_blocks, act);
 }
 
 int32_t katsu_conv_igemm_dx(katsu_cuda_ctx *ctx, const float *w, const float *gr, float *dx,
@@ -982,7 +1189,8 @@ int32_t katsu_conv_igemm_dx(katsu_cuda_ctx *ctx, const float *w, const float *gr
             bool ok = nhwc_map(&ma, gt, n, oh, ow, k, p.bw, p.bh, 1, CU_TENSOR_MAP_SWIZZLE_128B) &&
                       nhwc_map(&ma_lo, three ? gt_lo : gt, n, oh, ow, k, p.bw, p.bh, 1, CU_TENSOR_MAP_SWIZZLE_128B);
             if (!ok) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv dX)");
-            KATSU_TRY(launch_igemm(ctx, ma, ma_lo, wb, three ? wb_lo : wb, taps, c, k, p, total_blocks));
+            const Activation act = {gt, three ? gt_lo : gt, n, oh, ow, k, 1};
+            KATSU_TRY(launch_igemm(ctx, ma, ma_lo, wb, three ? wb_lo : wb, taps, c, k, p, total_blocks, act));
         }
     return KATSU_OK;
 }
@@ -1027,7 +1235,7 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr
     // (3xTF32, or channel counts that rule out one-load tiles: single-pass TF32 has no lo halves to save,
     // and with one load per operand tile its deep-ring kernel below is as fast or faster)
     const bool whole_groups = (c % 32 == 0) && (k % 32 == 0);
-    const bool via_gemm = !plan.all_taps && bnt == 128 && (three || !whole_groups);
+    const bool via_gemm = !plan.all_taps && bnt == 128 && !whole_groups;  // EXPERIMENT
     bool ok = nhwc_map(&mg, gt, n, oh, ow, k, 8, 4, 1, via_gemm ? CU_TENSOR_MAP_SWIZZLE_NONE : sw) &&
               nhwc_map(&mg_lo, three ? gt_lo : gt, n, oh, ow, k, 8, 4, 1, sw) &&
               nhwc_map(&mx, xt, n, h, wd, c, 8, 4, (int)stride, sw) &&

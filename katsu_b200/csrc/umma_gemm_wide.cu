@@ -3,12 +3,15 @@
 // Replaces, for KATSU_MODE_TF32 and large shapes, the loops of Tensor::matmul
 // (crates/katsu-core/src/tensor.rs:265-273) and of its VJP (tensor.rs:425-444).
 //
-// Why a kernel of its own.  A tcgen05 kind::tf32 MMA of one thread block runs at full rate only with
-// N = 256: back-to-back 128 x 128 x 8 MMAs issue every ~137 clocks, 128 x 256 x 8 ones every ~171, so the
-// 128 x 128 tiles of the split-precision kernel (umma_gemm.cu; its tensor-memory budget goes to the A stages
-// that 3xTF32 needs) cap single-pass TF32 at half of the pipe.  Single pass needs no lo halves and no A in
-// tensor memory: a stage is A (16 KiB) | B (32 KiB), four stages deep, and tensor memory holds two 256-column
-// accumulators so that a tile's epilogue runs under the next tile's k-loop.
+// Why a kernel of its own.  The split-precision kernel (umma_gemm.cu) routes A through tensor memory, where
+// builder threads split it into hi | lo, and spends its tensor-memory budget on those stages; in single-pass
+// mode that detour only costs time (the builders, not the pipe, set the pace: 358 TFLOP/s at 8192^3).  Single
+// pass needs no lo halves and no A in tensor memory: a stage is A (16 KiB) | B (32 KiB) read straight from shared
+// memory, four stages deep, and tensor memory holds two 256-column accumulators so that a tile's epilogue runs
+// under the next tile's k-loop.  The tile is 128 x 256 because what bounds the k-loop is the traffic through
+// shared memory (every operand byte is written once by TMA and read once per MMA that uses it): back-to-back
+// MMAs on resident operands run at the pipe's rate for N = 128 and N = 256 alike (64 and 128 clocks), but per
+// flop a 128 x 256 tile moves three quarters of the bytes of a 128 x 128 one.
 //
 // Persistent: one block per SM walks the tiles band by band (bands of RASTER_M tile rows, column-major
 // inside a band) so that blocks running together share operand tiles in L2.  Warps 0-3 are the epilogue
@@ -18,6 +21,7 @@
 
 #include "common.cuh"
 #include "sm100.cuh"
+#include "sm100_pair.cuh"
 
 using namespace sm100;
 
@@ -185,6 +189,179 @@ umma_gemm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     if (warp == 5) tmem_dealloc(tmem_base, 512);
 }
 
+// ---- the same on pairs of thread blocks: 256 x 256 tiles ---------------------------------------------
+// In the kernel above a stage's bytes cross the SM's shared memory twice, written by TMA and read by the MMAs
+// (12 KiB each per 128 x 256 x 8 MMA), and the k-loop runs at about 210 clocks per MMA against the pipe's 128.
+// With cta_group::2 one MMA spans two SMs: each block supplies its own 128 rows of A and HALF of the 256
+// columns of B, so a block moves 8 KiB in and 8 KiB out per MMA for the same tensor work.  Each block's tensor
+// memory holds its 128 rows of the result (two 256-column accumulators, alternating between tiles).
+//
+// Roles per block as above (warps 0-3 epilogue, warp 4 TMA, warp 5 MMA issue in the leader only).  Across the
+// pair: both blocks' loads complete on the LEADER's full barrier, the leader's commits release a stage and
+// publish an accumulator on both blocks' barriers, and both blocks' epilogue warps free an accumulator on the
+// leader's barrier.  Every wait is bounded; both blocks always reach the cluster barrier at the end.
+constexpr int PAIR_STAGES = 6, BH = BN / 2;
+constexpr int PAIR_B_BYTES = BH * BK * 4, PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;
+constexpr size_t PAIR_SMEM = size_t(PAIR_STAGES) * PAIR_STAGE_BYTES + 1024;
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+umma_gemm_wide_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                           const __grid_constant__ WideParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t full[PAIR_STAGES], empty[PAIR_STAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int kblocks = (p.K + BK - 1) / BK;
+    const int total_tiles = p.m_tiles * p.n_tiles;  // m_tiles counts 256-row pair tiles here
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int my_tiles = (total_tiles - pair + pairs - 1) / pairs;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s) {
+            mbar_init(&full[s], 1);    // the leader's: its own expect_tx arrival, both blocks' bytes
+            mbar_init(&empty[s], 1);   // each block's own copy, released by the leader's commit
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);   // each block's own copy
+            mbar_init(&acc_empty[b], 8);  // the leader's: four epilogue warps of each block
+        }
+        mbar_init_fence();
+    }
+    if (warp == 5) {
+        tmem_alloc_pair(&tmem_slot, 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();  // both blocks' barriers exist before anything is signalled across the pair
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 4 && lane == 0) {
+        // ---- TMA producer of this block's rows of A and half of B; bytes are counted on the leader's barrier ----
+        bool ok = true;
+        for (int it = 0; it < my_tiles && ok; ++it) {
+            int mt, nt;
+            tile_of(pair + it * pairs, p.m_tiles, p.n_tiles, &mt, &nt);
+            const int m0 = (2 * mt + (int)rank) * BM, nb0 = nt * BN + (int)rank * BH;
+            for (int i = 0; i < kblocks; ++i) {
+                const int g = it * kblocks + i, s = g % PAIR_STAGES;
+                if (g >= PAIR_STAGES && !mbar_wait(&empty[s], ((g / PAIR_STAGES) - 1) & 1, p.status, 141)) { ok = false; break; }
+                if (leader) mbar_arrive_expect_tx(&full[s], 2 * PAIR_STAGE_BYTES);
+                const uint32_t bar = map_to_rank(&full[s], 0);
+                unsigned char *ad = smem + s * PAIR_STAGE_BYTES, *bd = ad + A_BYTES;
+                const int k0 = i * BK;
+                if (!A_MN) {
+                    tma_load_2d_pair(ad, &map_a, bar, k0, m0);
+                } else if (p.a_grouped) {
+                    tma_load_3d_pair(ad, &map_a, bar, 0, k0, m0 / 32);
+                } else {
+                    for (int j = 0; j < BM / 32; ++j) tma_load_2d_pair(ad + j * 4096, &map_a, bar, m0 + 32 * j, k0);
+                }
+                if (!B_MN) {
+                    tma_load_2d_pair(bd, &map_b, bar, k0, nb0);
+                } else if (p.b_grouped) {
+                    tma_load_3d_pair(bd, &map_b, bar, 0, k0, nb0 / 32);
+                } else {
+                    for (int j = 0; j < BH / 32; ++j) tma_load_2d_pair(bd + j * 4096, &map_b, bar, nb0 + 32 * j, k0);
+                }
+            }
+        }
+    } else if (warp == 5 && leader) {
+        // ---- MMA issue for the pair: whole warp in the loop, the elect.sync thread issues ----
+        const bool issue = elect_one();
+        const uint32_t idesc = idesc_tf32(2 * BM, BN, A_MN, B_MN);
+        bool ok = true;
+        for (int it = 0; it < my_tiles && ok; ++it) {
+            const int b = it & 1;
+            if (it >= 2 && !mbar_wait_warp(&acc_empty[b], ((it >> 1) - 1) & 1, p.status, 144)) break;
+            tc_fence_after_sync();
+            const uint32_t acc = tmem_base + uint32_t(b) * BN;
+            for (int i = 0; i < kblocks; ++i) {
+                const int g = it * kblocks + i, s = g % PAIR_STAGES;
+                if (!mbar_wait_warp_ready(&full[s], (g / PAIR_STAGES) & 1, p.status, 142)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t ad = smem_u32(smem + s * PAIR_STAGE_BYTES), bd = ad + A_BYTES;
+                if (issue) {
+#pragma unroll
+                    for (int j = 0; j < BK / 8; ++j) {
+                        const uint64_t a_desc = A_MN ? smem_desc(ad + j * 1024, 4096, 512, kLayoutSw128Base32)
+                                                     : smem_desc(ad + j * 32, 16, 1024, kLayoutSw128);
+                        const uint64_t b_desc = B_MN ? smem_desc(bd + j * 1024, 4096, 512, kLayoutSw128Base32)
+                                                     : smem_desc(bd + j * 32, 16, 1024, kLayoutSw128);
+                        mma_tf32_pair(acc, a_desc, b_desc, idesc, !(i == 0 && j == 0));
+                    }
+                    // every release goes to this block's barrier and to the peer's copy of it
+                    mma_commit_pair(smem_u32(&empty[s]));
+                    mma_commit_pair(map_to_rank(&empty[s], 1));
+                    if (i == kblocks - 1) {
+                        mma_commit_pair(smem_u32(&acc_full[b]));
+                        mma_commit_pair(map_to_rank(&acc_full[b], 1));
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp < 4) {
+        // ---- epilogue: thread = row of this block's half of the tile ----
+        const bool vec = (p.N & 3) == 0;
+        for (int it = 0; it < my_tiles; ++it) {
+            const int b = it & 1;
+            if (!mbar_wait_warp(&acc_full[b], (it >> 1) & 1, p.status, 143)) break;
+            tc_fence_after_sync();
+            int mt, nt;
+            tile_of(pair + it * pairs, p.m_tiles, p.n_tiles, &mt, &nt);
+            const int row = (2 * mt + (int)rank) * BM + warp * 32 + lane, n0 = nt * BN;
+            float *dst_row = p.c + size_t(row < p.M ? row : 0) * p.N;
+            const uint32_t acc = tmem_base + (uint32_t(warp * 32) << 16) + uint32_t(b) * BN;
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                const bool last_group = c0 + 32 >= BN || n0 + c0 + 32 >= p.N;
+                float v[32];
+                tmem_ld_32x32(acc + c0, v);
+                if (last_group) {
+                    // everything this tile needs from the accumulator is in registers now
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (leader) mbar_arrive(&acc_empty[b]);
+                        else mbar_arrive_cluster(map_to_rank(&acc_empty[b], 0));
+                    }
+                }
+                if (row < p.M) {
+                    float *dst = dst_row + n0 + c0;
+                    if (vec && n0 + c0 + 32 <= p.N) {
+                        float4 *d4 = reinterpret_cast<float4 *>(dst);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                            if (p.accumulate) {
+                                const float4 old = d4[i];
+                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                            }
+                            d4[i] = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (n0 + c0 + i < p.N) dst[i] = p.accumulate ? dst[i] + v[i] : v[i];
+                    }
+                }
+                if (last_group) break;
+            }
+        }
+    }
+    // Neither block leaves (or gives its tensor memory back) while the other may still signal its barriers,
+    // read its half of B or hold accumulators: every path above ends here.
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 5) tmem_dealloc_pair(tmem_base, 512);
+}
+
 bool wide_map(CUtensorMap *map, const float *base, bool mn_major, size_t mn_extent, size_t k_extent, uint32_t tile,
               int *grouped) {
     *grouped = 0;
@@ -227,6 +404,43 @@ int32_t launch_wide(katsu_cuda_ctx *ctx, const float *a, const float *b, float *
     return KATSU_OK;
 }
 
+template <bool A_MN, bool B_MN>
+int32_t launch_wide_pair(katsu_cuda_ctx *ctx, const float *a, const float *b, float *c, size_t M, size_t N, size_t K,
+                         int accumulate) {
+    WideParams p;
+    CUtensorMap map_a, map_b;
+    if (!wide_map(&map_a, a, A_MN, M, K, BM, &p.a_grouped) || !wide_map(&map_b, b, B_MN, N, K, BH, &p.b_grouped))
+        return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed for a matmul operand");
+    p.c = c;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.m_tiles = (int)katsu_div_up(M, (size_t)(2 * BM));
+    p.n_tiles = (int)katsu_div_up(N, (size_t)BN);
+    p.accumulate = accumulate;
+    p.status = ctx->status;
+    auto kernel = umma_gemm_wide_pair_kernel<A_MN, B_MN>;
+    KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
+    size_t pairs = size_t(p.m_tiles) * p.n_tiles;
+    if (pairs > (size_t)ctx->num_sms / 2) pairs = (size_t)ctx->num_sms / 2;
+    cudaLaunchConfig_t config;
+    memset(&config, 0, sizeof(config));
+    config.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    config.blockDim = dim3(192, 1, 1);
+    config.dynamicSmemBytes = PAIR_SMEM;
+    config.stream = ctx->stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = 2;
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    cudaError_t err = cudaLaunchKernelEx(&config, kernel, map_a, map_b, p);
+    ctx->launches += 1;
+    if (err != cudaSuccess)
+        return katsu_set_error(KATSU_ERR_CUDA, "pair GEMM launch failed: %s", cudaGetErrorString(err));
+    return KATSU_OK;
+}
+
 }  // namespace
 
 // C[M,N] (+)= A * B in single-pass TF32 with 128 x 256 tiles.  *handled = 0 unless the context is in
@@ -241,6 +455,14 @@ int32_t katsu_umma_gemm_wide(katsu_cuda_ctx *ctx, const float *a, const float *b
     if (tiles * 2 < (size_t)ctx->num_sms || tiles > 0x3fffffffu) return KATSU_OK;
     if (katsu_div_up(K, (size_t)BK) * tiles > 0x7fffffffu) return KATSU_OK;  // the ring counter is an int
     *handled = 1;
+    // tall enough for 256-row tiles on pairs of thread blocks, and enough of them for every pair of SMs
+    const size_t pair_tiles = katsu_div_up(M, (size_t)(2 * BM)) * katsu_div_up(N, (size_t)BN);
+    if (M >= 256 && pair_tiles * 2 >= (size_t)ctx->num_sms / 2) {
+        if (!a_mn && !b_mn) return launch_wide_pair<false, false>(ctx, a, b, c, M, N, K, accumulate);
+        if (!a_mn && b_mn) return launch_wide_pair<false, true>(ctx, a, b, c, M, N, K, accumulate);
+        if (a_mn && !b_mn) return launch_wide_pair<true, false>(ctx, a, b, c, M, N, K, accumulate);
+        return launch_wide_pair<true, true>(ctx, a, b, c, M, N, K, accumulate);
+    }
     if (!a_mn && !b_mn) return launch_wide<false, false>(ctx, a, b, c, M, N, K, accumulate);
     if (!a_mn && b_mn) return launch_wide<false, true>(ctx, a, b, c, M, N, K, accumulate);
     if (a_mn && !b_mn) return launch_wide<true, false>(ctx, a, b, c, M, N, K, accumulate);

@@ -37,6 +37,10 @@ SHAPES = [
     # three channels with 65..128 output channels: the dX kernel's filter operand takes three or four
     # 8 KiB blocks and it runs with three g stages so that its shared memory still fits the SM
     (1, 3, 16, 32, 96, 3, 3, 1, 1), (2, 3, 30, 36, 128, 3, 3, 1, 1), (1, 2, 20, 40, 80, 3, 3, 1, 1),
+    # 256 or more channels on a side: 128 x 256 tiles with drained accumulators (forward when K >= 256, dX when
+    # C >= 256), ragged pixel tiles, a stride, and an output-channel count that is not a whole number of
+    # 32-channel groups (dW then keeps the kernel that loads operand tiles slab by slab)
+    (1, 256, 9, 10, 256, 3, 3, 1, 1), (2, 64, 6, 7, 512, 3, 3, 2, 1), (1, 512, 8, 8, 272, 1, 1, 1, 0),
 ]
 
 
@@ -76,7 +80,8 @@ def test_conv_matches_oracle(ctx, oracle, shape, accumulate):
 
 
 @pytest.mark.parametrize("shape", [(2, 32, 14, 14, 48, 3, 3, 1, 1), (1, 64, 16, 16, 32, 3, 3, 2, 1),
-                                   (2, 3, 40, 64, 48, 3, 3, 1, 1)],
+                                   (2, 3, 40, 64, 48, 3, 3, 1, 1), (1, 256, 9, 10, 256, 3, 3, 1, 1),
+                                   (2, 320, 6, 6, 256, 3, 3, 1, 1)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_conv_tf32_mode(ctx, oracle, shape):
     """Opt-in single-pass TF32 mode on the tensor-core path: within 2e-3, and measurably

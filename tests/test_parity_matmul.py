@@ -61,12 +61,15 @@ def test_same_buffer_for_both_gradients(ctx, oracle, size, accumulate):
         assert_parity(d.get("d"), expect, 2 * size, what=("same parent", size, accumulate))
 
 
-@pytest.mark.parametrize("shape", [(1100, 2080, 2304), (1152, 520, 2332)], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("shape", [(1100, 2080, 2304), (1152, 520, 2332), (200, 96, 19200)],
+                         ids=lambda s: "x".join(map(str, s)))
 @pytest.mark.parametrize("accumulate", [0, 1])
 def test_large_single_pass_tf32(ctx, oracle, shape, accumulate):
-    """Shapes with at least one 128 x 256 tile per two SMs take the single-pass kernel that reads both operands
-    from shared memory: all four operand layouts (c: K-major x MN-major, dA: K x K, dB: MN x MN), ragged
-    edges in every dimension, and (second shape) an N that is not a whole number of 32-column groups."""
+    """Shapes with at least one 128 x 256 tile per two SMs take the single-pass kernels that read both operands
+    from shared memory (256 x 256 tiles on pairs of thread blocks when there are 256 rows or more, else
+    128 x 256): all four operand layouts (c: K-major x MN-major, dA: K x K, dB: MN x MN), ragged edges in
+    every dimension, an N that is not a whole number of 32-column groups (second shape), and fewer than 256
+    rows (third shape: the one-block kernel)."""
     m, k, n = shape
     rng = np.random.default_rng(m + k + n + accumulate)
     a = rng.standard_normal(m * k).astype(np.float32)
