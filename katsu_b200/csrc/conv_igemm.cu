@@ -105,6 +105,12 @@ struct IgemmParams {
     int accumulate, three_pass;
     int *status;
     short off_y[MAX_TAPS], off_x[MAX_TAPS], b_tap[MAX_TAPS];
+    // merge_x = 1 (dX of a stride-2 layer): every pixel tile is computed twice in a row, once per x-parity
+    // class (the second with the tap table below), into the two accumulator sets; the epilogue keeps the first
+    // class's results in registers and writes the two results of a pixel pair side by side (output x = 2 jx
+    // and 2 jx + 1).  One launch per class left every 32-byte sector of dX half written, twice.
+    int merge_x, ntaps2, grid_w2;
+    short off_y2[MAX_TAPS], off_x2[MAX_TAPS], b_tap2[MAX_TAPS];
 };
 
 // Persistent: one block per SM walks (pixel tile, channel tile) pairs.  BNT = 128 / 64 / 32 output
@@ -131,7 +137,7 @@ struct IgemmCfg {
     static_assert(SINGLE || BNT <= 128, "the split-precision stage of a 256-wide tile does not fit twice");
 };
 
-template <int BNT, bool SINGLE>
+template <int BNT, bool SINGLE, bool MERGE>
 __global__ void __launch_bounds__(192, 1)
 conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_lo,
                   const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_b_lo,
@@ -146,9 +152,11 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int blocks_per_img = p.blocks_x * p.blocks_y;
     const int kchunks = (p.kc + BK - 1) / BK;
-    const int kblocks = p.ntaps * kchunks;
+    const int kblocks_cls[2] = {p.ntaps * kchunks, p.ntaps2 * kchunks};
     const int total_tiles = m_tiles * n_tiles;
-    const int my_tiles = (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    // passes over the accumulator sets: one per tile, or two per tile (class 0, class 1) with merge_x
+    constexpr int shift = MERGE ? 1 : 0;
+    const int my_tiles = ((total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x) << shift;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES_T; ++s) {
@@ -173,8 +181,10 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (warp == 4 && lane == 0) {
         // ---- TMA producer ----
         bool ok = true;
+        int g = 0;  // stages filled so far
         for (int it = 0; it < my_tiles && ok; ++it) {
-            const int tile = blockIdx.x + it * gridDim.x;
+            const int tile = blockIdx.x + (it >> shift) * gridDim.x, cls = it & shift;
+            const int kblocks = kblocks_cls[cls];
             const int mt = tile / n_tiles, n0 = (tile % n_tiles) * BNT;
             // block coordinates of the tile's two 64-pixel halves
             int bn[2], by[2], bx[2];
@@ -185,19 +195,21 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 by[h] = r / p.blocks_x;
                 bx[h] = r % p.blocks_x;
             }
-            for (int i = 0; i < kblocks; ++i) {
-                const int g = it * kblocks + i, s = g % STAGES_T;
+            for (int i = 0; i < kblocks; ++i, ++g) {
+                const int s = g % STAGES_T;
                 if (g >= STAGES_T && !mbar_wait(&empty[s], ((g / STAGES_T) - 1) & 1, p.status, 21)) { ok = false; break; }
                 mbar_arrive_expect_tx(&full[s], PARTS * (TILE_BYTES + Cfg::B_BYTES));
                 unsigned char *st = smem + s * Cfg::STAGE_BYTES;
                 const int t = i / kchunks, k0 = (i % kchunks) * BK;
+                const int ox = cls ? p.off_x2[t] : p.off_x[t], oy = cls ? p.off_y2[t] : p.off_y[t];
+                const int bt = cls ? p.b_tap2[t] : p.b_tap[t];
                 for (int part = 0; part < PARTS; ++part) {
                     const CUtensorMap *ma = part ? &map_a_lo : &map_a;
                     const CUtensorMap *mb = part ? &map_b_lo : &map_b;
                     for (int h = 0; h < 2; ++h)
                         tma_load_4d(st + part * TILE_BYTES + h * (TILE_BYTES / 2), ma, &full[s], k0,
-                                    bx[h] * p.bw * p.in_step + p.off_x[t], by[h] * p.bh * p.in_step + p.off_y[t], bn[h]);
-                    tma_load_4d(st + Cfg::B_OFF + part * Cfg::B_BYTES, mb, &full[s], k0, n0, p.b_tap[t], 0);
+                                    bx[h] * p.bw * p.in_step + ox, by[h] * p.bh * p.in_step + oy, bn[h]);
+                    tma_load_4d(st + Cfg::B_OFF + part * Cfg::B_BYTES, mb, &full[s], k0, n0, bt, 0);
                 }
             }
         }
@@ -207,12 +219,14 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const bool issue = elect_one();
         const uint32_t idesc = idesc_tf32(BM, BNT, false, false);
         bool ok = true;
+        int g = 0;  // stages consumed so far
         for (int it = 0; it < my_tiles && ok; ++it) {
             const int b = it & 1;
+            const int kblocks = kblocks_cls[it & shift];
             if (it >= 2 && !mbar_wait_warp(&acc_empty[b], ((it >> 1) - 1) & 1, p.status, 24)) break;
             tc_fence_after_sync();
-            for (int i = 0; i < kblocks; ++i) {
-                const int g = it * kblocks + i, s = g % STAGES_T;
+            for (int i = 0; i < kblocks; ++i, ++g) {
+                const int s = g % STAGES_T;
                 if (!mbar_wait_warp_ready(&full[s], (g / STAGES_T) & 1, p.status, 22)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t st = smem_u32(smem + s * Cfg::STAGE_BYTES);
@@ -243,12 +257,17 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // ---- epilogue: thread = pixel; accumulators summed in registers, 32 channels at a time ----
         const int r = warp * 32 + lane;
         const size_t plane = size_t(p.out_h) * p.out_w;
-        const int used_acc = kblocks < NACC_T ? kblocks : NACC_T;
+        // merge_x: the first class's results of this thread's pixel, kept until the second class's are ready
+        constexpr int HELD = MERGE ? BNT : 1;
+        float held[HELD];
         for (int it = 0; it < my_tiles; ++it) {
             const int b = it & 1;
+            const int cls = it & shift;
+            const int kblocks = kblocks_cls[cls];
+            const int used_acc = kblocks < NACC_T ? kblocks : NACC_T;
             if (!mbar_wait_warp(&acc_full[b], (it >> 1) & 1, p.status, 23)) break;
             tc_fence_after_sync();
-            const int tile = blockIdx.x + it * gridDim.x;
+            const int tile = blockIdx.x + (it >> shift) * gridDim.x;
             const int mt = tile / n_tiles, n0 = (tile % n_tiles) * BNT;
             const long long gb = 2ll * mt + (r >> 6);
             const int img = int(gb / blocks_per_img);
@@ -259,6 +278,47 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const int oy = p.out_sy * jy + p.out_oy, ox = p.out_sx * jx + p.out_ox;
             float *dst_px = p.out + size_t(img) * p.out_c * plane + size_t(oy) * p.out_w + ox;
             const uint32_t set = tmem_base + (uint32_t(warp * 32) << 16) + uint32_t(b) * Cfg::SET_COLS;
+            if constexpr (MERGE) {
+                {
+                    // pixel pair (oy, 2 jx), (oy, 2 jx + 1): class 0 is held, class 1 completes the pair
+                    const bool ok2 = pixel_ok && jx < p.grid_w2;
+                    const bool vec = ok2 && ((p.out_w & 1) == 0) && !p.accumulate;
+#pragma unroll
+                    for (int c0 = 0; c0 < BNT; c0 += 32) {
+                        float v[32];
+                        tmem_ld_32x32(set + c0, v);
+                        for (int a = 1; a < used_acc; ++a) {
+                            float t[32];
+                            tmem_ld_32x32(set + a * BNT + c0, t);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] += t[i];
+                        }
+                        if (c0 + 32 >= BNT) {
+                            tc_fence_before_sync();
+                            mbar_arrive(&acc_empty[b]);
+                        }
+                        if (cls == 0) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) held[c0 + i] = v[i];
+                        } else if (pixel_ok) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                const int ch = n0 + c0 + i;
+                                if (ch < p.out_c) {
+                                    float *dst = dst_px + size_t(ch) * plane;
+                                    if (vec) {
+                                        *reinterpret_cast<float2 *>(dst) = make_float2(held[c0 + i], v[i]);
+                                    } else {
+                                        dst[0] = p.accumulate ? dst[0] + held[c0 + i] : held[c0 + i];
+                                        if (ok2) dst[1] = p.accumulate ? dst[1] + v[i] : v[i];
+                                    }
+                                }
+                            }
+                        }
+                    }
+                    continue;
+                }
+            }
             for (int c0 = 0; c0 < BNT; c0 += 32) {
                 const bool last_group = c0 + 32 >= BNT || n0 + c0 + 32 >= p.out_c;
                 float v[32];
@@ -1009,7 +1069,8 @@ int32_t launch_igemm_bn(katsu_cuda_ctx *ctx, const CUtensorMap &ma, const CUtens
     CUtensorMap mb, mb_lo;
     if (!taps_map(&mb, b_hi, taps, rows, inner, BNT) || !taps_map(&mb_lo, b_lo, taps, rows, inner, BNT))
         return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv weights)");
-    auto kernel = conv_igemm_kernel<BNT, SINGLE>;
+    auto kernel = p.merge_x ? conv_igemm_kernel<BNT, SINGLE, (BNT <= 128)> : conv_igemm_kernel<BNT, SINGLE, false>;
+    if (p.merge_x && BNT > 128) return katsu_set_error(KATSU_ERR_UNSUPPORTED, "merged dX classes need tiles of at most 128 channels");
     KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)IgemmCfg<BNT, SINGLE>::SMEM));
     const size_t m_tiles = katsu_div_up(total_blocks, 2), n_tiles = katsu_div_up(rows, (size_t)BNT);
     if (m_tiles * n_tiles > 0x7fffffffu / 64) return katsu_set_error(KATSU_ERR_UNSUPPORTED, "convolution too large for the tile counter");
@@ -1095,6 +1156,7 @@ int32_t katsu_conv_igemm_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w
     p.accumulate = 0;
     p.three_pass = three ? 1 : 0;
     p.status = ctx->status;
+    p.merge_x = 0; p.ntaps2 = 0; p.grid_w2 = 0;
     for (size_t t = 0; t < taps; ++t) {
         p.off_y[t] = (short)((int)(t / s) - (int)pad);
         p.off_x[t] = (short)((int)(t % s) - (int)pad);
@@ -1152,9 +1214,60 @@ int32_t katsu_conv_igemm_dx(katsu_cuda_ctx *ctx, const float *w, const float *gr
         KATSU_CUDA_TRY(cudaMemsetAsync(dx, 0, n * c * h * wd * sizeof(float), ctx->stream));
         accumulate = 1;
     }
+    // taps of parity class (py, px) into the given tables; returns their number
+    auto class_taps = [&](int py, int px, short *oy, short *ox, short *bt) {
+        int nt = 0;
+        for (int ky = 0; ky < (int)r; ++ky) {
+            const int ty = py + (int)pad - ky;
+            if (((ty % st) + st) % st != 0) continue;
+            for (int kx = 0; kx < (int)s; ++kx) {
+                const int tx = px + (int)pad - kx;
+                if (((tx % st) + st) % st != 0) continue;
+                // floor division (ty, tx may be negative)
+                oy[nt] = (short)((ty >= 0) ? ty / st : -((-ty + st - 1) / st));
+                ox[nt] = (short)((tx >= 0) ? tx / st : -((-tx + st - 1) / st));
+                bt[nt] = (short)(ky * (int)s + kx);
+                ++nt;
+            }
+        }
+        return nt;
+    };
+    // Stride 2, every class reached by some tap, tiles of at most 128 channels: one launch per ROW parity
+    // computes both x-parity classes and writes them interleaved (IgemmParams::merge_x).
+    if (st == 2 && !some_class_empty && wd >= 2 && !wide_tiles_pay(c)) {
+        for (int py = 0; py < 2 && py < (int)h; ++py) {
+            IgemmParams p;
+            p.out = dx;
+            p.n_img = (int)n; p.out_c = (int)c; p.out_h = (int)h; p.out_w = (int)wd;
+            p.grid_h = (int)((h - py + 1) / 2);
+            p.grid_w = (int)((wd + 1) / 2);
+            p.grid_w2 = (int)(wd / 2);
+            pick_block((size_t)p.grid_w, &p.bw, &p.bh);
+            p.blocks_x = (p.grid_w + p.bw - 1) / p.bw;
+            p.blocks_y = (p.grid_h + p.bh - 1) / p.bh;
+            p.out_sy = 2; p.out_oy = py; p.out_sx = 2; p.out_ox = 0;
+            p.in_step = 1;
+            p.kc = (int)k;
+            p.accumulate = accumulate;
+            p.three_pass = three ? 1 : 0;
+            p.status = ctx->status;
+            p.merge_x = 1;
+            p.ntaps = class_taps(py, 0, p.off_y, p.off_x, p.b_tap);
+            p.ntaps2 = class_taps(py, 1, p.off_y2, p.off_x2, p.b_tap2);
+            const size_t total_blocks = n * p.blocks_x * p.blocks_y;
+            CUtensorMap ma, ma_lo;
+            bool ok = nhwc_map(&ma, gt, n, oh, ow, k, p.bw, p.bh, 1, CU_TENSOR_MAP_SWIZZLE_128B) &&
+                      nhwc_map(&ma_lo, three ? gt_lo : gt, n, oh, ow, k, p.bw, p.bh, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+            if (!ok) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv dX)");
+            const Activation act = {gt, three ? gt_lo : gt, n, oh, ow, k, 1};
+            KATSU_TRY(launch_igemm(ctx, ma, ma_lo, wb, three ? wb_lo : wb, taps, c, k, p, total_blocks, act));
+        }
+        return KATSU_OK;
+    }
     for (int py = 0; py < st && py < (int)h; ++py)
         for (int px = 0; px < st && px < (int)wd; ++px) {
             IgemmParams p;
+            p.merge_x = 0; p.ntaps2 = 0; p.grid_w2 = 0;
             p.out = dx;
             p.n_img = (int)n; p.out_c = (int)c; p.out_h = (int)h; p.out_w = (int)wd;
             p.grid_h = (int)((h - py + st - 1) / st);
@@ -1168,20 +1281,7 @@ int32_t katsu_conv_igemm_dx(katsu_cuda_ctx *ctx, const float *w, const float *gr
             p.accumulate = accumulate;
             p.three_pass = three ? 1 : 0;
             p.status = ctx->status;
-            int nt = 0;
-            for (int ky = 0; ky < (int)r; ++ky) {
-                const int ty = py + (int)pad - ky;
-                if (((ty % st) + st) % st != 0) continue;
-                for (int kx = 0; kx < (int)s; ++kx) {
-                    const int tx = px + (int)pad - kx;
-                    if (((tx % st) + st) % st != 0) continue;
-                    // floor division (ty, tx may be negative)
-                    p.off_y[nt] = (short)((ty >= 0) ? ty / st : -((-ty + st - 1) / st));
-                    p.off_x[nt] = (short)((tx >= 0) ? tx / st : -((-tx + st - 1) / st));
-                    p.b_tap[nt] = (short)(ky * (int)s + kx);
-                    ++nt;
-                }
-            }
+            const int nt = class_taps(py, px, p.off_y, p.off_x, p.b_tap);
             p.ntaps = nt;
             if (nt == 0) continue;
             const size_t total_blocks = n * p.blocks_x * p.blocks_y;
