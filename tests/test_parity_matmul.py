@@ -96,6 +96,31 @@ def test_large_single_pass_tf32(ctx, oracle, shape, accumulate):
         assert np.max(np.abs(got - ref)) <= max_abs_bound(ref, terms, unit=TF32_UNIT, sqrt_terms=False)
 
 
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_large_split_precision(ctx, oracle, accumulate):
+    """At least one 256 x 256 tile per pair of SMs in the default mode: the kernel that reads both operands and
+    their lo halves from shared memory on pairs of thread blocks, with alternating drained accumulators.  All
+    three products of this shape take it (K-major x MN-major, K x K, MN x MN); N is ragged and not a whole
+    number of 32-column groups.  Held to the 1e-5 bar against the exact (f64) products."""
+    m, k, n = 2100, 2304, 2332
+    rng = np.random.default_rng(77 + accumulate)
+    a = rng.standard_normal(m * k).astype(np.float32)
+    b = rng.standard_normal(k * n).astype(np.float32)
+    g = rng.standard_normal(m * n).astype(np.float32)
+    da0 = rng.standard_normal(m * k).astype(np.float32) if accumulate else np.zeros(m * k, np.float32)
+    db0 = rng.standard_normal(k * n).astype(np.float32) if accumulate else np.zeros(k * n, np.float32)
+    c64 = oracle.matmul_f64(a, b, m, k, n)
+    da64, db64 = oracle.matmul_backward_f64(a, b, g, m, k, n)
+    with DeviceArrays(ctx, a=a, b=b, g=g, da=da0, db=db0) as d:
+        d.alloc("c", m * n, fill=np.nan)
+        ctx.matmul_fwd(d["a"], d["b"], d["c"], m, k, n)
+        ctx.matmul_bwd(d["a"], d["b"], d["g"], d["da"], d["db"], m, k, n, accumulate)
+        c, da, db = d.get("c"), d.get("da"), d.get("db")
+    assert_parity(c, c64, k, what="c")
+    assert_parity(da, da0.astype(np.float64) + da64, n, what="da")
+    assert_parity(db, db0.astype(np.float64) + db64, m, what="db")
+
+
 @pytest.mark.parametrize("mode,bar", [(1, 2e-3), (2, REL_L2_TOL)], ids=["tf32", "fp32"])
 def test_matmul_precision_modes(ctx, oracle, mode, bar):
     """TF32 mode (one tensor-core pass) holds the 2e-3 bar; FP32 mode stays on CUDA cores."""
