@@ -237,6 +237,52 @@ pub fn conv2d_forward(ctx: &Context, x: &DeviceBuf, w: &DeviceBuf, bias: Option<
     })
 }
 
+/// Size in floats of the channels-innermost copy of x that this geometry's kernels read in the context's
+/// current precision mode; 0 when they read x directly.
+pub fn conv2d_staged_len(ctx: &Context, g: &ConvGeometry) -> Result<usize, CudaError> {
+    let mut floats: usize = 0;
+    check(unsafe {
+        ffi::katsu_cuda_conv2d_staged_floats(ctx.ptr(), g.batch, g.cin, g.h, g.w, g.cout, g.kh, g.kw, g.stride, g.padding,
+                                             &mut floats)
+    })?;
+    Ok(floats)
+}
+
+/// Writes that copy.  `Conv2D` holds its input from forward to backward (conv2d.rs:104-107, 130-136); holding
+/// this copy beside it lets both calls skip their own staging pass.
+pub fn conv2d_stage(ctx: &Context, x: &DeviceBuf, staged: &mut DeviceBuf, g: &ConvGeometry) -> Result<(), CudaError> {
+    length("x", x, g.x_len())?;
+    length("staged", staged, conv2d_staged_len(ctx, g)?)?;
+    check(unsafe { ffi::katsu_cuda_conv2d_stage(ctx.ptr(), x.ptr, staged.ptr, g.batch, g.cin, g.h, g.w) })
+}
+
+/// `conv2d_forward` reading x through its staged copy (bit-identical to the plain call).
+pub fn conv2d_forward_staged(ctx: &Context, x: &DeviceBuf, staged: Option<&DeviceBuf>, w: &DeviceBuf, bias: Option<&DeviceBuf>,
+                             relu: bool, y: &mut DeviceBuf, g: &ConvGeometry) -> Result<(), CudaError> {
+    length("x", x, g.x_len())?;
+    length("w", w, g.w_len())?;
+    length("y", y, g.y_len())?;
+    check(unsafe {
+        ffi::katsu_cuda_conv2d_fwd_staged(ctx.ptr(), x.ptr, opt_const(staged), w.ptr, opt_const(bias), y.ptr, g.batch, g.cin,
+                                          g.h, g.w, g.cout, g.kh, g.kw, g.stride, g.padding, relu as i32)
+    })
+}
+
+/// `conv2d_backward` reading x through its staged copy (dW).
+pub fn conv2d_backward_staged(ctx: &Context, x: &DeviceBuf, staged: Option<&DeviceBuf>, w: &DeviceBuf, grad: &DeviceBuf,
+                              scale: Option<GradScale<'_>>, dx: Option<&mut DeviceBuf>, dw: Option<&mut DeviceBuf>,
+                              g: &ConvGeometry, accumulate: bool) -> Result<(), CudaError> {
+    length("x", x, g.x_len())?;
+    length("w", w, g.w_len())?;
+    length("grad", grad, g.y_len())?;
+    let (scalar, factor) = scale.map_or((ptr::null(), 1.0), |s| (opt_const(s.scalar), s.factor));
+    check(unsafe {
+        ffi::katsu_cuda_conv2d_bwd_staged(ctx.ptr(), x.ptr, opt_const(staged), w.ptr, grad.ptr, scalar, factor, opt_mut(dx),
+                                          opt_mut(dw), g.batch, g.cin, g.h, g.w, g.cout, g.kh, g.kw, g.stride, g.padding,
+                                          accumulate as i32)
+    })
+}
+
 /// Scale of the upstream gradient handed to `conv2d_backward`: the gradient is `factor * scalar[0] * g`
 /// without being stored (what the VJP of `sum(y * y)` sends: g = y, factor 2, scalar = the loss adjoint).
 pub struct GradScale<'a> {

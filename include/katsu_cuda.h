@@ -134,6 +134,28 @@ int32_t katsu_cuda_conv2d_bwd_scaled(katsu_cuda_ctx *ctx, const float *x, const 
 int32_t katsu_cuda_conv2d_fwd_bias_relu(katsu_cuda_ctx *ctx, const float *x, const float *w, const float *bias,
                                         float *y, size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r,
                                         size_t s, size_t stride, size_t pad, int32_t relu);
+/* The layer's input staged once for forward and backward.  Conv2D keeps its input between forward and
+ * backward (crates/katsu-core/src/conv2d.rs:104-107, 130-136); the wide-channel kernels of both read x
+ * through a channels-innermost copy that each call otherwise writes for itself.  A caller that holds x
+ * anyway can hold that copy too:
+ *   katsu_cuda_conv2d_staged_floats  *floats = size of the copy for this shape in the context's CURRENT
+ *                                    precision mode, 0 when the shape's kernels use none;
+ *   katsu_cuda_conv2d_stage          writes it into `staged` (device memory of that many floats);
+ *   katsu_cuda_conv2d_fwd_staged     katsu_cuda_conv2d_fwd_bias_relu reading x through x_staged;
+ *   katsu_cuda_conv2d_bwd_staged     katsu_cuda_conv2d_bwd_scaled reading x through x_staged (dW).
+ * x_staged may be null (the plain calls).  The copy is only valid for the precision mode, x contents and
+ * shape it was written for; results are bit-identical to the plain calls. */
+int32_t katsu_cuda_conv2d_staged_floats(katsu_cuda_ctx *ctx, size_t n, size_t c, size_t h, size_t wd, size_t k,
+                                        size_t r, size_t s, size_t stride, size_t pad, size_t *floats);
+int32_t katsu_cuda_conv2d_stage(katsu_cuda_ctx *ctx, const float *x, float *staged, size_t n, size_t c, size_t h,
+                                size_t wd);
+int32_t katsu_cuda_conv2d_fwd_staged(katsu_cuda_ctx *ctx, const float *x, const float *x_staged, const float *w,
+                                     const float *bias, float *y, size_t n, size_t c, size_t h, size_t wd,
+                                     size_t k, size_t r, size_t s, size_t stride, size_t pad, int32_t relu);
+int32_t katsu_cuda_conv2d_bwd_staged(katsu_cuda_ctx *ctx, const float *x, const float *x_staged, const float *w,
+                                     const float *g, const float *gscale, float gfactor, float *dx, float *dw,
+                                     size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                                     size_t stride, size_t pad, int32_t accumulate);
 /* Backward of that epilogue over y_act [n, k, plane]: dg = g where y_act > 0 else 0 (relu != 0;
  * dg may alias g, or be null when only dbias is wanted), dbias[k] (+)= sum over n and the plane of
  * dg (null: skipped).  With relu == 0 the gradient passes through unchanged: pass dg = null and

@@ -50,6 +50,10 @@ SIGNATURES = {
     "katsu_cuda_conv2d_bwd": [_ctx, _ptr, _ptr, _ptr, _ptr, _ptr] + [_sz] * 9 + [_i32],
     "katsu_cuda_conv2d_bwd_scaled": [_ctx, _ptr, _ptr, _ptr, _ptr, ctypes.c_float, _ptr, _ptr] + [_sz] * 9 + [_i32],
     "katsu_cuda_conv2d_fwd_bias_relu": [_ctx, _ptr, _ptr, _ptr, _ptr] + [_sz] * 9 + [_i32],
+    "katsu_cuda_conv2d_staged_floats": [_ctx] + [_sz] * 9 + [ctypes.POINTER(ctypes.c_size_t)],
+    "katsu_cuda_conv2d_stage": [_ctx, _ptr, _ptr, _sz, _sz, _sz, _sz],
+    "katsu_cuda_conv2d_fwd_staged": [_ctx, _ptr, _ptr, _ptr, _ptr, _ptr] + [_sz] * 9 + [_i32],
+    "katsu_cuda_conv2d_bwd_staged": [_ctx, _ptr, _ptr, _ptr, _ptr, _ptr, ctypes.c_float, _ptr, _ptr] + [_sz] * 9 + [_i32],
     "katsu_cuda_bias_relu_bwd": [_ctx, _ptr, _ptr, _ptr, _ptr, _sz, _sz, _sz, _i32, _i32],
     "katsu_cuda_sgd_step": [_ctx, _ptr, _ptr, ctypes.c_float, _sz],
     "katsu_cuda_sumsq": [_ctx, _ptr, _ptr, _sz],
@@ -227,6 +231,23 @@ class Context:
 
     def conv2d_bwd(self, x, w, g, dx, dw, n, c, h, wd, k, r, s, stride, pad, accumulate=0) -> None:
         self.call("katsu_cuda_conv2d_bwd", x, w, g, dx, dw, n, c, h, wd, k, r, s, stride, pad, accumulate)
+
+    def conv2d_staged_floats(self, n, c, h, wd, k, r, s, stride, pad) -> int:
+        """Floats of the channels-innermost copy of x that this shape's kernels read (0: none)."""
+        out = ctypes.c_size_t(0)
+        self.call("katsu_cuda_conv2d_staged_floats", n, c, h, wd, k, r, s, stride, pad, ctypes.byref(out))
+        return int(out.value)
+
+    def conv2d_stage(self, x, staged, n, c, h, wd) -> None:
+        self.call("katsu_cuda_conv2d_stage", x, staged, n, c, h, wd)
+
+    def conv2d_fwd_staged(self, x, x_staged, w, bias, y, n, c, h, wd, k, r, s, stride, pad, relu=0) -> None:
+        self.call("katsu_cuda_conv2d_fwd_staged", x, x_staged, w, bias, y, n, c, h, wd, k, r, s, stride, pad, relu)
+
+    def conv2d_bwd_staged(self, x, x_staged, w, g, gscale, gfactor, dx, dw, n, c, h, wd, k, r, s, stride, pad,
+                          accumulate=0) -> None:
+        self.call("katsu_cuda_conv2d_bwd_staged", x, x_staged, w, g, gscale, gfactor, dx, dw, n, c, h, wd, k, r, s,
+                  stride, pad, accumulate)
 
     def matmul_fwd(self, a, b, c, m, k, n) -> None:
         self.call("katsu_cuda_matmul_fwd", a, b, c, m, k, n)

@@ -26,6 +26,10 @@ struct katsu_cuda_ctx {
     // set by conv2d_bwd while one call computes both dX and dW on the implicit-GEMM path: the dX
     // launch stages g (channels-innermost copy) where the dW launch expects it, once for both
     int share_g_staging, g_staged;
+    // set by the *_staged entry points for the duration of one call: the caller's channels-innermost copy
+    // of x (hi, then lo in 3xTF32 mode), written by katsu_cuda_conv2d_stage; the forward and dW launches use
+    // it instead of staging x themselves
+    const float *x_prestaged;
     // Buffer written by katsu_cuda_flush_l2.
     float *flush;
     size_t flush_floats;
@@ -148,6 +152,12 @@ int32_t katsu_umma_conv_dw(katsu_cuda_ctx *ctx, const CUtensorMap_st *map_g, con
 
 // Wide-channel implicit-GEMM convolution on the tensor cores (conv_igemm.cu); *handled = 0
 // when the shape is outside what it takes.
+// Floats of the staging copy of x that the implicit-GEMM kernels use for this shape in the context's precision
+// mode (0 when the shape takes other kernels), and the pass that writes it.
+size_t katsu_conv_igemm_staged_floats(const katsu_cuda_ctx *ctx, size_t n, size_t c, size_t h, size_t wd, size_t k,
+                                      size_t r, size_t s, size_t stride, size_t pad, size_t oh, size_t ow);
+int32_t katsu_conv_igemm_stage(katsu_cuda_ctx *ctx, const float *x, float *staged, size_t n, size_t c, size_t h,
+                               size_t wd);
 int32_t katsu_conv_igemm_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,
                              size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
                              size_t stride, size_t pad, size_t oh, size_t ow, int *handled);

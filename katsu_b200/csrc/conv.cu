@@ -127,6 +127,50 @@ extern "C" int32_t katsu_cuda_conv2d_fwd_bias_relu(katsu_cuda_ctx *ctx, const fl
     return forward(ctx, x, w, bias, y, n, c, h, wd, k, r, s, stride, pad, relu ? 1 : 0);
 }
 
+// ---- the layer's input staged once for forward and backward ---------------------------------------------
+// Conv2D keeps its input between forward and backward (crates/katsu-core/src/conv2d.rs:104-107, 130-136), and
+// the wide-channel kernels of both read x through a channels-innermost copy: a caller that holds the input
+// anyway can hold that copy too and pay for the pass once per step instead of twice.
+extern "C" int32_t katsu_cuda_conv2d_staged_floats(katsu_cuda_ctx *ctx, size_t n, size_t c, size_t h, size_t wd, size_t k,
+                                                   size_t r, size_t s, size_t stride, size_t pad, size_t *floats) {
+    KATSU_REQUIRE(ctx != nullptr && floats != nullptr, "null argument");
+    Geometry g;
+    KATSU_TRY(geometry(c, h, wd, k, r, s, stride, pad, &g));
+    *floats = 0;
+    if (n == 0) return KATSU_OK;
+    *floats = katsu_conv_igemm_staged_floats(ctx, n, c, h, wd, k, r, s, stride, pad, g.oh, g.ow);
+    return KATSU_OK;
+}
+
+extern "C" int32_t katsu_cuda_conv2d_stage(katsu_cuda_ctx *ctx, const float *x, float *staged, size_t n, size_t c,
+                                           size_t h, size_t wd) {
+    KATSU_TRY(katsu_bind(ctx));
+    KATSU_REQUIRE(x != nullptr && staged != nullptr, "null tensor");
+    KATSU_REQUIRE(n > 0 && c > 0 && h > 0 && wd > 0, "empty input");
+    return katsu_conv_igemm_stage(ctx, x, staged, n, c, h, wd);
+}
+
+extern "C" int32_t katsu_cuda_conv2d_fwd_staged(katsu_cuda_ctx *ctx, const float *x, const float *x_staged, const float *w,
+                                                const float *bias, float *y, size_t n, size_t c, size_t h, size_t wd,
+                                                size_t k, size_t r, size_t s, size_t stride, size_t pad, int32_t relu) {
+    KATSU_REQUIRE(ctx != nullptr, "null context");
+    ctx->x_prestaged = x_staged;
+    const int32_t rc = forward(ctx, x, w, bias, y, n, c, h, wd, k, r, s, stride, pad, relu ? 1 : 0);
+    ctx->x_prestaged = nullptr;
+    return rc;
+}
+
+extern "C" int32_t katsu_cuda_conv2d_bwd_staged(katsu_cuda_ctx *ctx, const float *x, const float *x_staged, const float *w,
+                                                const float *gr, const float *gscale, float gfactor, float *dx, float *dw,
+                                                size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
+                                                size_t stride, size_t pad, int32_t accumulate) {
+    KATSU_REQUIRE(ctx != nullptr, "null context");
+    ctx->x_prestaged = x_staged;
+    const int32_t rc = backward(ctx, x, w, gr, gscale, gfactor, dx, dw, n, c, h, wd, k, r, s, stride, pad, accumulate);
+    ctx->x_prestaged = nullptr;
+    return rc;
+}
+
 extern "C" int32_t katsu_cuda_conv2d_bwd(katsu_cuda_ctx *ctx, const float *x, const float *w, const float *gr,
                                          float *dx, float *dw,
                                          size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,

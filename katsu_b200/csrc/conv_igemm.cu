@@ -1124,6 +1124,19 @@ int32_t launch_igemm(katsu_cuda_ctx *ctx, const CUtensorMap &ma, const CUtensorM
 
 }  // namespace
 
+size_t katsu_conv_igemm_staged_floats(const katsu_cuda_ctx *ctx, size_t n, size_t c, size_t h, size_t wd, size_t k,
+                                      size_t r, size_t s, size_t stride, size_t pad, size_t oh, size_t ow) {
+    const Shape g = {n, c, h, wd, k, r, s, stride, pad, oh, ow};
+    if (!igemm_shape(ctx, g)) return 0;
+    return padded(n * c * h * wd) * (ctx->precision == KATSU_MODE_3XTF32 ? 2 : 1);
+}
+
+int32_t katsu_conv_igemm_stage(katsu_cuda_ctx *ctx, const float *x, float *staged, size_t n, size_t c, size_t h,
+                               size_t wd) {
+    const bool three = ctx->precision == KATSU_MODE_3XTF32;
+    return stage_nhwc(ctx, x, staged, three ? staged + padded(n * c * h * wd) : nullptr, n, c, h * wd);
+}
+
 int32_t katsu_conv_igemm_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w, float *y,
                              size_t n, size_t c, size_t h, size_t wd, size_t k, size_t r, size_t s,
                              size_t stride, size_t pad, size_t oh, size_t ow, int *handled) {
@@ -1138,7 +1151,12 @@ int32_t katsu_conv_igemm_fwd(katsu_cuda_ctx *ctx, const float *x, const float *w
     Scratch sc = {base, 0};
     float *xt = sc.take(xe), *xt_lo = three ? sc.take(xe) : nullptr;
     float *wf = sc.take(we), *wf_lo = three ? sc.take(we) : nullptr;
-    KATSU_TRY(stage_nhwc(ctx, x, xt, xt_lo, n, c, h * wd));
+    if (ctx->x_prestaged != nullptr) {
+        xt = const_cast<float *>(ctx->x_prestaged);
+        xt_lo = three ? xt + padded(xe) : nullptr;
+    } else {
+        KATSU_TRY(stage_nhwc(ctx, x, xt, xt_lo, n, c, h * wd));
+    }
     KATSU_LAUNCH(ctx, weights_to_taps_kernel, (unsigned)katsu_div_up(we, 256), 256, 0, w, wf, wf_lo, (float *)nullptr,
                  (float *)nullptr, (int)k, (int)c, (int)taps);
 
@@ -1325,7 +1343,12 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr
     float *gt = sc.take(ge), *gt_lo = three ? sc.take(ge) : nullptr;
     float *xt = sc.take(xe), *xt_lo = three ? sc.take(xe) : nullptr;
     p.partial = sc.take(plan.partial_floats);
-    KATSU_TRY(stage_nhwc(ctx, x, xt, xt_lo, n, c, h * wd));
+    if (ctx->x_prestaged != nullptr) {
+        xt = const_cast<float *>(ctx->x_prestaged);
+        xt_lo = three ? xt + padded(xe) : nullptr;
+    } else {
+        KATSU_TRY(stage_nhwc(ctx, x, xt, xt_lo, n, c, h * wd));
+    }
     if (!ctx->g_staged) KATSU_TRY(stage_nhwc(ctx, gr, gt, gt_lo, n, k, oh * ow));
 
     CUtensorMap mg, mg_lo, mx, mx_lo;

@@ -143,6 +143,11 @@ struct TensorNode {
     mutable std::vector<float> host;
     mutable bool host_valid = false;
     mutable std::shared_ptr<DeviceBuffer> dev;  // null until uploaded / computed
+    // channels-innermost copy of the values for the wide-channel convolution kernels, written when a Conv2D
+    // first reads this tensor as its input and reused by that layer's backward (values never change);
+    // staged_mode is the precision mode it was written in
+    mutable std::shared_ptr<DeviceBuffer> staged;
+    mutable int staged_mode = -1;
     // values are parents[0] * parents[0], not computed yet (set by Tensor::mul when fusion is on)
     mutable bool lazy_square = false;
     mutable std::shared_ptr<DeviceBuffer> grad_dev;  // null == None (unless grad_sym holds it)
@@ -242,6 +247,26 @@ Tensor Tensor::zeros(const std::vector<size_t> &shape) {
         fail(ErrorKind::Allocation, e.what());
     }
     return from_vec(std::move(data), shape);
+}
+
+// The staged copy of a convolution's input for the given geometry, written on first use; null when the
+// shape's kernels read x directly.
+static const float *staged_input(const Tensor &x, size_t n, size_t c, size_t h, size_t w, size_t k, size_t r, size_t s,
+                                 size_t stride, size_t padding) {
+    katsu_cuda_ctx *ctx = device_context();
+    size_t floats = 0;
+    check(katsu_cuda_conv2d_staged_floats(ctx, n, c, h, w, k, r, s, stride, padding, &floats));
+    if (floats == 0) return nullptr;
+    int32_t mode = 0;
+    check(katsu_cuda_get_precision(ctx, &mode));
+    const TensorNode &node = *x.node();
+    if (!node.staged || node.staged->count != floats || node.staged_mode != mode) {
+        auto buffer = std::make_shared<DeviceBuffer>(floats);
+        check(katsu_cuda_conv2d_stage(ctx, x.device_data(), buffer->ptr, n, c, h, w));
+        node.staged = std::move(buffer);
+        node.staged_mode = mode;
+    }
+    return node.staged->ptr;
 }
 
 Tensor Tensor::make_node(std::shared_ptr<DeviceBuffer> data, std::vector<size_t> shape, Op op,
@@ -458,17 +483,18 @@ void op_backward(const Tensor &node, Adjoint &own, Pending &pending, Touched &to
             if (x.id() != w.id()) {
                 // backward_buffers + `pending[parent] += grad` (tensor.rs:374-390)
                 const int acc_x = touched.count(x.id()) ? 1 : 0, acc_w = touched.count(w.id()) ? 1 : 0;
+                const float *xs_staged = staged_input(x, xs[0], xs[1], xs[2], xs[3], ws[0], ws[2], ws[3], op.stride, op.padding);
                 if (acc_x == acc_w) {
-                    check(katsu_cuda_conv2d_bwd_scaled(ctx, x.device_data(), w.device_data(), g, gscale, gfactor, px, pw,
-                                                       xs[0], xs[1], xs[2], xs[3], ws[0], ws[2], ws[3], op.stride,
+                    check(katsu_cuda_conv2d_bwd_staged(ctx, x.device_data(), xs_staged, w.device_data(), g, gscale, gfactor,
+                                                       px, pw, xs[0], xs[1], xs[2], xs[3], ws[0], ws[2], ws[3], op.stride,
                                                        op.padding, acc_x));
                 } else {
-                    check(katsu_cuda_conv2d_bwd_scaled(ctx, x.device_data(), w.device_data(), g, gscale, gfactor, px,
-                                                       nullptr, xs[0], xs[1], xs[2], xs[3], ws[0], ws[2], ws[3], op.stride,
-                                                       op.padding, acc_x));
-                    check(katsu_cuda_conv2d_bwd_scaled(ctx, x.device_data(), w.device_data(), g, gscale, gfactor, nullptr,
-                                                       pw, xs[0], xs[1], xs[2], xs[3], ws[0], ws[2], ws[3], op.stride,
-                                                       op.padding, acc_w));
+                    check(katsu_cuda_conv2d_bwd_staged(ctx, x.device_data(), xs_staged, w.device_data(), g, gscale, gfactor,
+                                                       px, nullptr, xs[0], xs[1], xs[2], xs[3], ws[0], ws[2], ws[3],
+                                                       op.stride, op.padding, acc_x));
+                    check(katsu_cuda_conv2d_bwd_staged(ctx, x.device_data(), xs_staged, w.device_data(), g, gscale, gfactor,
+                                                       nullptr, pw, xs[0], xs[1], xs[2], xs[3], ws[0], ws[2], ws[3],
+                                                       op.stride, op.padding, acc_w));
                 }
                 touched.insert(x.id());
                 touched.insert(w.id());
@@ -690,11 +716,15 @@ Tensor Conv2D::forward(const Tensor &input) {
     const Geometry geometry(input, weights_, stride_, padding_);
     const std::vector<size_t> shape = geometry.output_shape();
     auto out = std::make_shared<DeviceBuffer>(element_count(shape));
-    if (out->count != 0)
-        check(katsu_cuda_conv2d_fwd_bias_relu(device_context(), input.device_data(), weights_.device_data(),
-                                              bias_.defined() ? bias_.device_data() : nullptr, out->ptr, geometry.batch,
-                                              geometry.cin, geometry.h, geometry.w, geometry.cout, geometry.kh,
-                                              geometry.kw, stride_, padding_, relu_ ? 1 : 0));
+    if (out->count != 0) {
+        // the input is read through its staged copy, which the backward pass of this layer finds again
+        const float *staged = staged_input(input, geometry.batch, geometry.cin, geometry.h, geometry.w, geometry.cout,
+                                           geometry.kh, geometry.kw, stride_, padding_);
+        check(katsu_cuda_conv2d_fwd_staged(device_context(), input.device_data(), staged, weights_.device_data(),
+                                           bias_.defined() ? bias_.device_data() : nullptr, out->ptr, geometry.batch,
+                                           geometry.cin, geometry.h, geometry.w, geometry.cout, geometry.kh,
+                                           geometry.kw, stride_, padding_, relu_ ? 1 : 0));
+    }
     Op op;
     op.kind = Op::Conv2D;
     op.stride = stride_;
@@ -728,9 +758,11 @@ std::pair<Tensor, Tensor> Conv2D::backward(const Tensor &grad_output) const {
                                        geometry.cout, geometry.oh * geometry.ow, 1, 0));
         g = masked->ptr;
     }
-    check(katsu_cuda_conv2d_bwd(device_context(), input.device_data(), weights_.device_data(),
-                                g, dx->ptr, dw->ptr, geometry.batch, geometry.cin, geometry.h,
-                                geometry.w, geometry.cout, geometry.kh, geometry.kw, stride_, padding_, 0));
+    const float *staged = staged_input(input, geometry.batch, geometry.cin, geometry.h, geometry.w, geometry.cout,
+                                       geometry.kh, geometry.kw, stride_, padding_);
+    check(katsu_cuda_conv2d_bwd_staged(device_context(), input.device_data(), staged, weights_.device_data(), g, nullptr,
+                                       1.f, dx->ptr, dw->ptr, geometry.batch, geometry.cin, geometry.h, geometry.w,
+                                       geometry.cout, geometry.kh, geometry.kw, stride_, padding_, 0));
     return {Tensor::make_node(std::move(dx), input.shape(), Op{}, {}),
             Tensor::make_node(std::move(dw), weights_.shape(), Op{}, {})};
 }
