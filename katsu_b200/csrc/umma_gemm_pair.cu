@@ -437,8 +437,9 @@ int32_t katsu_umma_gemm_pair(katsu_cuda_ctx *ctx, const float *a, const float *b
                              bool a_mn, bool b_mn, int accumulate, int *handled) {
     *handled = 0;
     // Measured at 8192^3 / 4096^3: 238 / 229-234 TFLOP/s useful in 3xTF32 against 206-219 / 199-207 for the
-    // single-block kernel; in single-pass TF32 the pair ring is slower (279 / 333 against 337-358 / 310-327),
-    // so that mode stays on the single-block kernel.
+    // single-block kernel.  Shapes with a 256 x 256 tile for every pair of SMs have been taken by
+    // umma_gemm_wide.cu before this is called (both modes); what arrives here in 3xTF32 is the rest with 256
+    // rows or more, which needs this kernel's K split to fill the GPU.
     if (ctx->precision != KATSU_MODE_3XTF32) return KATSU_OK;
     if (M < 256 || N < 64 || K < 32) return KATSU_OK;
     if (katsu_div_up(M, (size_t)(2 * BM)) * katsu_div_up(N, (size_t)BN) > 0x3fffffffu) return KATSU_OK;
