@@ -41,6 +41,8 @@ SHAPES = [
     # C >= 256), ragged pixel tiles, a stride, and an output-channel count that is not a whole number of
     # 32-channel groups (dW then keeps the kernel that loads operand tiles slab by slab)
     (1, 256, 9, 10, 256, 3, 3, 1, 1), (2, 64, 6, 7, 512, 3, 3, 2, 1), (1, 512, 8, 8, 272, 1, 1, 1, 0),
+    # dW with 256-wide input-channel tiles whose second tile is a quarter full, half of an output-channel tile
+    (2, 320, 6, 6, 64, 3, 3, 1, 1),
 ]
 
 
