@@ -82,78 +82,96 @@ gemm_strided_kernel(const float *__restrict__ a, const float *__restrict__ b, fl
 }
 
 // ---------------------------------------------------------------------------
-// skinny forward, n <= NP <= 16.  grid = (row blocks of 32, k splits).  Each
-// warp owns 4 rows; lanes walk the split's k range four columns at a time
-// (one float4 of a per row).  The matching [KC x n] slab of b is staged in
-// shared memory.  Partials go to scratch as [split][m][n]; a second kernel
-// folds the splits in order.
+// skinny forward, n <= NP <= 16.  grid = (k slabs of SK_KC columns, row splits).
+// A block stages its [SK_KC x n] slab of b in shared memory once, then streams
+// its rows of a: a warp takes four rows at a time, its lanes cover the slab's
+// columns as float4s (all sixteen loads of an iteration are issued before the
+// first use, which is what keeps enough bytes in flight for HBM), and the
+// per-row sums over the slab go to scratch as [slab][m][n]; a second kernel
+// folds the slabs in order.
 // ---------------------------------------------------------------------------
-constexpr int SK_KC = 512;   // k columns per shared-memory slab
-constexpr int SK_RW = 4;     // rows per warp
+constexpr int SK_RW = 4;     // rows per warp and iteration
+// k columns per shared-memory slab: as many as 48 KiB hold, at most 1024.  A longer slab means fewer
+// cross-lane reductions (one per row and slab) for the same bytes of a.
+template <int NP>
+constexpr int sk_kc() { return NP <= 12 ? 1024 : 512; }
 
 template <int NP>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 skinny_fwd_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ partial,
-                  int m, size_t k, int n, size_t k_per_split, int vec_ok) {
-    __shared__ float bs[SK_KC * NP];
+                  int m, size_t k, int n, int rows_per_block, int vec_ok) {
+    // the slab transposed, [NP][SK_KC]: a lane's four consecutive k for one output column are one 128-bit
+    // shared-memory read, and consecutive lanes read consecutive float4s (the [k][n] order put sixteen lanes
+    // on one bank)
+    constexpr int SK_KC = sk_kc<NP>();
+    __shared__ __align__(16) float bs[NP * SK_KC];
     const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
-    const int row0 = blockIdx.x * 32 + wp * SK_RW;
-    const size_t k_begin = size_t(blockIdx.y) * k_per_split;
-    size_t k_end = k_begin + k_per_split;
-    if (k_end > k) k_end = k;
-    float acc[SK_RW][NP];
-#pragma unroll
-    for (int r = 0; r < SK_RW; ++r)
-#pragma unroll
-        for (int j = 0; j < NP; ++j) acc[r][j] = 0.f;
-
-    for (size_t kc = k_begin; kc < k_end; kc += SK_KC) {
-        const int span = (int)((k_end - kc) < (size_t)SK_KC ? (k_end - kc) : (size_t)SK_KC);
-        __syncthreads();
-        for (int e = tid; e < SK_KC * NP; e += 256) {
-            const int pp = e / NP, j = e % NP;
-            bs[e] = (pp < span && j < n) ? __ldg(b + (kc + pp) * n + j) : 0.f;
+    const size_t kc = size_t(blockIdx.x) * SK_KC;
+    const int span = (int)((k - kc) < (size_t)SK_KC ? (k - kc) : (size_t)SK_KC);
+    // rows kc .. kc + span of b are one contiguous run of span * n floats: read it in order (coalesced),
+    // scatter into the transposed slab; columns n .. NP and rows past the end of k are zero
+    for (int e = tid; e < SK_KC * NP; e += 256) bs[e] = 0.f;
+    __syncthreads();
+    {
+        const float *slab = b + kc * n;
+        const int count = span * n;
+        for (int e = tid; e < count; e += 256) {
+            const int pp = e / n, j = e - pp * n;
+            bs[j * SK_KC + pp] = __ldg(slab + e);
         }
-        __syncthreads();
-        for (int pp = lane * 4; pp < span; pp += 128) {
-            float av[SK_RW][4];
+    }
+    __syncthreads();
+    const int r_begin = blockIdx.y * rows_per_block;
+    const int r_end = (r_begin + rows_per_block) < m ? (r_begin + rows_per_block) : m;
+    const bool whole = vec_ok && span == SK_KC;
+    for (int row0 = r_begin + wp * SK_RW; row0 < r_end; row0 += 8 * SK_RW) {
+        float acc[SK_RW][NP];
+#pragma unroll
+        for (int r = 0; r < SK_RW; ++r)
+#pragma unroll
+            for (int j = 0; j < NP; ++j) acc[r][j] = 0.f;
+        for (int base = 0; base < SK_KC; base += 512) {   // sixteen loads in flight per lane at a time
+        float av[4][SK_RW][4];
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int pp = base + lane * 4 + it * 128;
 #pragma unroll
             for (int r = 0; r < SK_RW; ++r) {
                 const int row = row0 + r;
-                if (row < m) {
-                    const float *src = a + size_t(row) * k + kc + pp;
-                    if (vec_ok && pp + 3 < span) {
-                        const float4 q = __ldg(reinterpret_cast<const float4 *>(src));
-                        av[r][0] = q.x; av[r][1] = q.y; av[r][2] = q.z; av[r][3] = q.w;
-                    } else {
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) av[r][u] = (pp + u < span) ? __ldg(src + u) : 0.f;
-                    }
+                const float *src = a + size_t(row < r_end ? row : r_begin) * k + kc + pp;
+                if (whole) {
+                    const float4 q = __ldg(reinterpret_cast<const float4 *>(src));
+                    av[it][r][0] = q.x; av[it][r][1] = q.y; av[it][r][2] = q.z; av[it][r][3] = q.w;
                 } else {
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) av[r][u] = 0.f;
+                    for (int u = 0; u < 4; ++u) av[it][r][u] = (pp + u < span) ? __ldg(src + u) : 0.f;
                 }
             }
+        }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                float bv[NP];
+        for (int it = 0; it < 4; ++it) {
+            const int pp = base + lane * 4 + it * 128;
 #pragma unroll
-                for (int j = 0; j < NP; ++j) bv[j] = bs[(pp + u) * NP + j];
+            for (int j = 0; j < NP; ++j) {
+                const float4 bq = *reinterpret_cast<const float4 *>(&bs[j * SK_KC + pp]);
+                const float bv[4] = {bq.x, bq.y, bq.z, bq.w};
+                // k order within the lane as before: u = 0, 1, 2, 3
 #pragma unroll
-                for (int r = 0; r < SK_RW; ++r)
+                for (int u = 0; u < 4; ++u)
 #pragma unroll
-                    for (int j = 0; j < NP; ++j) acc[r][j] = fmaf(av[r][u], bv[j], acc[r][j]);
+                    for (int r = 0; r < SK_RW; ++r) acc[r][j] = fmaf(av[it][r][u], bv[u], acc[r][j]);
             }
         }
+        }  // halves of the slab
+#pragma unroll
+        for (int r = 0; r < SK_RW; ++r)
+#pragma unroll
+            for (int j = 0; j < NP; ++j) {
+                const float sum = warp_sum(acc[r][j]);
+                const int row = row0 + r;
+                if (lane == 0 && row < r_end && j < n) partial[(size_t(blockIdx.x) * m + row) * n + j] = sum;
+            }
     }
-#pragma unroll
-    for (int r = 0; r < SK_RW; ++r)
-#pragma unroll
-        for (int j = 0; j < NP; ++j) {
-            const float s = warp_sum(acc[r][j]);
-            const int row = row0 + r;
-            if (lane == 0 && row < m && j < n) partial[(size_t(blockIdx.y) * m + row) * n + j] = s;
-        }
 }
 
 // out[i] (+)= sum over `parts` slabs of `elems` floats, in slab order.
@@ -162,7 +180,16 @@ fold_partials_kernel(const float *__restrict__ partial, float *out, size_t elems
     const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= elems) return;
     float s = 0.f;
-    for (int p = 0; p < parts; ++p) s += partial[size_t(p) * elems + i];
+    int p = 0;
+    // sixteen loads in flight, added in slab order (a plain loop waits out one L2 round trip per slab)
+    for (; p + 16 <= parts; p += 16) {
+        float v[16];
+#pragma unroll
+        for (int q = 0; q < 16; ++q) v[q] = __ldg(partial + size_t(p + q) * elems + i);
+#pragma unroll
+        for (int q = 0; q < 16; ++q) s += v[q];
+    }
+    for (; p < parts; ++p) s += partial[size_t(p) * elems + i];
     out[i] = accumulate ? out[i] + s : s;
 }
 
@@ -220,14 +247,18 @@ skinny_da_kernel(const float *__restrict__ g, const float *__restrict__ b, float
 // ---------------------------------------------------------------------------
 // skinny dB: db[p, j] (+)= sum_i a[i,p] * g[i,j].  A thread owns four
 // consecutive p and NP columns; it streams its float4 column strip of a over
-// the block's row range.  grid = (k / 512, row splits); partials [split][k][n]
-// go to scratch and are folded in order.
+// the block's row range, eight rows per iteration with all eight loads issued
+// before the first use.  The g rows of the range sit in shared memory
+// (broadcast reads).  grid = (k / 512, row splits); partials [split][k][n] go
+// to scratch and are folded in order.
 // ---------------------------------------------------------------------------
+constexpr int SK_GROWS = 256;  // g rows staged at a time
+
 template <int NP>
 __global__ void __launch_bounds__(128)
 skinny_db_kernel(const float *__restrict__ a, const float *__restrict__ g, float *__restrict__ partial, int m,
                  size_t k, int n, int rows_per_split, int vec_ok) {
-    __shared__ __align__(16) float gs[64 * NP];
+    __shared__ __align__(16) float gs[SK_GROWS * NP];
     const int tid = threadIdx.x;
     const size_t p = (size_t(blockIdx.x) * 128 + tid) * 4;
     const int r_begin = blockIdx.y * rows_per_split;
@@ -238,30 +269,39 @@ skinny_db_kernel(const float *__restrict__ a, const float *__restrict__ g, float
     for (int u = 0; u < 4; ++u)
 #pragma unroll
         for (int j = 0; j < NP; ++j) acc[u][j] = 0.f;
-    for (int rc = r_begin; rc < r_end; rc += 64) {
-        const int rows = (r_end - rc) < 64 ? (r_end - rc) : 64;
+    for (int rc = r_begin; rc < r_end; rc += SK_GROWS) {
+        const int rows = (r_end - rc) < SK_GROWS ? (r_end - rc) : SK_GROWS;
         __syncthreads();
-        for (int e = tid; e < 64 * NP; e += 128) {
+        for (int e = tid; e < SK_GROWS * NP; e += 128) {
             const int r = e / NP, j = e % NP;
             gs[e] = (r < rows && j < n) ? __ldg(g + size_t(rc + r) * n + j) : 0.f;
         }
         __syncthreads();
         if (p < k) {
-            for (int r = 0; r < rows; ++r) {
-                const float *src = a + size_t(rc + r) * k + p;
-                float av[4];
-                if (full) {
-                    const float4 q = __ldg(reinterpret_cast<const float4 *>(src));
-                    av[0] = q.x; av[1] = q.y; av[2] = q.z; av[3] = q.w;
-                } else {
+            for (int r0 = 0; r0 < rows; r0 += 8) {
+                float av[8][4];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) av[u] = (p + u < k) ? __ldg(src + u) : 0.f;
+                for (int q = 0; q < 8; ++q) {
+                    const int r = r0 + q;
+                    const float *src = a + size_t(rc + (r < rows ? r : 0)) * k + p;
+                    if (full) {
+                        const float4 v = __ldg(reinterpret_cast<const float4 *>(src));
+                        av[q][0] = v.x; av[q][1] = v.y; av[q][2] = v.z; av[q][3] = v.w;
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) av[q][u] = (p + u < k) ? __ldg(src + u) : 0.f;
+                    }
                 }
 #pragma unroll
-                for (int j = 0; j < NP; ++j) {
-                    const float gv = gs[r * NP + j];
+                for (int q = 0; q < 8; ++q) {
+                    if (r0 + q < rows) {
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) acc[u][j] = fmaf(av[u], gv, acc[u][j]);
+                        for (int j = 0; j < NP; ++j) {
+                            const float gv = gs[(r0 + q) * NP + j];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) acc[u][j] = fmaf(av[q][u], gv, acc[u][j]);
+                        }
+                    }
                 }
             }
         }
@@ -293,20 +333,21 @@ int32_t gemm_strided(katsu_cuda_ctx *ctx, const float *a, const float *b, float 
 
 template <int NP>
 int32_t skinny_fwd(katsu_cuda_ctx *ctx, const float *a, const float *b, float *c, size_t m, size_t k, size_t n) {
-    const size_t row_blocks = katsu_div_up(m, 32);
-    size_t splits = katsu_div_up(size_t(ctx->num_sms) * 4, row_blocks);
-    const size_t max_splits = katsu_div_up(k, (size_t)SK_KC);
-    if (splits > max_splits) splits = max_splits;
-    if (splits > 65535) splits = 65535;
-    size_t k_per_split = katsu_div_up(katsu_div_up(k, splits), (size_t)SK_KC) * SK_KC;
-    splits = katsu_div_up(k, k_per_split);
+    // one block per (slab of SK_KC columns, range of rows); the row ranges only exist to fill the GPU
+    const size_t slabs = katsu_div_up(k, (size_t)sk_kc<NP>());
+    size_t row_splits = katsu_div_up(size_t(ctx->num_sms) * 2, slabs);
+    const size_t max_row_splits = katsu_div_up(m, (size_t)(8 * SK_RW));
+    if (row_splits > max_row_splits) row_splits = max_row_splits;
+    if (row_splits > 65535) row_splits = 65535;
+    const size_t rows_per_block = katsu_div_up(katsu_div_up(m, row_splits), (size_t)(8 * SK_RW)) * (8 * SK_RW);
+    row_splits = katsu_div_up(m, rows_per_block);
     float *partial = nullptr;
-    KATSU_TRY(katsu_scratch(ctx, splits * m * n, &partial));
+    KATSU_TRY(katsu_scratch(ctx, slabs * m * n, &partial));
     const int vec_ok = aligned16(a) && (k % 4 == 0);
-    dim3 grid((unsigned)row_blocks, (unsigned)splits);
-    KATSU_LAUNCH(ctx, skinny_fwd_kernel<NP>, grid, 256, 0, a, b, partial, (int)m, k, (int)n, k_per_split, vec_ok);
+    dim3 grid((unsigned)slabs, (unsigned)row_splits);
+    KATSU_LAUNCH(ctx, skinny_fwd_kernel<NP>, grid, 256, 0, a, b, partial, (int)m, k, (int)n, (int)rows_per_block, vec_ok);
     KATSU_LAUNCH(ctx, fold_partials_kernel, (unsigned)katsu_div_up(m * n, 256), 256, 0, partial, c, m * n,
-                 (int)splits, 0);
+                 (int)slabs, 0);
     return KATSU_OK;
 }
 
@@ -340,8 +381,10 @@ int32_t skinny_db(katsu_cuda_ctx *ctx, const float *a, const float *g, float *db
 }
 
 bool skinny_shape(size_t m, size_t k, size_t n) {
+    // (the forward kernel keeps one [m x n] partial per 512-column slab of k: at most 256 MiB of scratch)
     return n >= 1 && n <= 16 && k >= 2048 && m <= 0x7fffffff && katsu_div_up(k, 512) <= 0x7fffffff &&
-           katsu_div_up(m, 32) <= 0x7fffffff && katsu_div_up(m, 64) <= 65535;
+           katsu_div_up(m, 32) <= 0x7fffffff && katsu_div_up(m, 64) <= 65535 &&
+           katsu_div_up(k, 512) * m * n <= (size_t(1) << 26);
 }
 
 }  // namespace
