@@ -766,6 +766,7 @@ struct DwTapsParams {
     int stride;
     int three_pass;
     int a_groups;               // 32-channel groups of g that exist (ceil(k / 32))
+    int grouped;                // 1: the g maps are 5-D (channel groups as a dimension): one load for the g tile
     int *status;
     short off_y[TAPS_MAX], off_x[TAPS_MAX];
 };
@@ -834,8 +835,12 @@ conv_dw_taps_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_cons
                 for (int part = 0; part < parts; ++part) {
                     const CUtensorMap *mg = part ? &map_g_lo : &map_g;
                     const CUtensorMap *mx = part ? &map_x_lo : &map_x;
-                    for (int j = 0; j < p.a_groups; ++j)
-                        tma_load_4d(st + part * a_bytes + j * 4096, mg, &full[s], 32 * j, ox0, oy0, img);
+                    if (p.grouped) {
+                        tma_load_5d(st + part * a_bytes, mg, &full[s], 0, ox0, oy0, 0, img);
+                    } else {
+                        for (int j = 0; j < p.a_groups; ++j)
+                            tma_load_4d(st + part * a_bytes + j * 4096, mg, &full[s], 32 * j, ox0, oy0, img);
+                    }
                     for (int t = 0; t < p.taps; ++t)
                         tma_load_4d(st + 2 * a_bytes + part * b_bytes + t * 4096, mx, &full[s], 0,
                                     ox0 * p.stride + p.off_x[t], oy0 * p.stride + p.off_y[t], img);
@@ -1390,6 +1395,15 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr
         q.three_pass = three ? 1 : 0;
         q.a_groups = (int)katsu_div_up(k, (size_t)32);
         q.status = ctx->status;
+        q.grouped = 0;
+        if (k % 32 == 0) {
+            // box = exactly the groups that exist, so the bytes counted on the stage barrier stay a_groups * 4 KiB
+            CUtensorMap ng, ng_lo;
+            if (nhwc_grouped_map(&ng, gt, n, oh, ow, k, 8, 4, 1, q.a_groups, sw) &&
+                nhwc_grouped_map(&ng_lo, three ? gt_lo : gt, n, oh, ow, k, 8, 4, 1, q.a_groups, sw)) {
+                mg = ng; mg_lo = ng_lo; q.grouped = 1;
+            }
+        }
         for (size_t t = 0; t < taps; ++t) { q.off_y[t] = p.off_y[t]; q.off_x[t] = p.off_x[t]; }
         const size_t smem = size_t(TAPS_STAGES) * (2 * TILE_BYTES + 2 * taps * 4096) + 1024;
         KATSU_CUDA_TRY(cudaFuncSetAttribute(conv_dw_taps_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
