@@ -702,6 +702,13 @@ int32_t katsu_umma_gemm_wide(katsu_cuda_ctx *ctx, const float *a, const float *b
         const size_t tiles3 = katsu_div_up(M, (size_t)(2 * BM)) * katsu_div_up(N, (size_t)BN);
         if (M < 256 || N < 256 || K < 32 || tiles3 < (size_t)ctx->num_sms / 2 || tiles3 > 0x3fffffffu) return KATSU_OK;
         if (katsu_div_up(K, (size_t)BK) * tiles3 > 0x7fffffffu) return KATSU_OK;
+        // room for the lo halves of both operands; without it the tensor-memory pair kernel (which needs b's
+        // only) takes the shape
+        float *room = nullptr;
+        if (katsu_scratch(ctx, M * K + K * N + 128, &room) != KATSU_OK) {
+            cudaGetLastError();
+            return KATSU_OK;
+        }
         *handled = 1;
         if (!a_mn && !b_mn) return launch_wide3_pair<false, false>(ctx, a, b, c, M, N, K, accumulate);
         if (!a_mn && b_mn) return launch_wide3_pair<false, true>(ctx, a, b, c, M, N, K, accumulate);
