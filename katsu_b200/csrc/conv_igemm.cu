@@ -366,17 +366,27 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 // overlap and the loop ran at 2480 clocks per 32 channels.
 constexpr int BK3 = 16;
 constexpr int DRAIN3 = 32;  // k-blocks of 16 channels
-constexpr int WIDE3_STAGES = 4;
-constexpr int WIDE3_A_BYTES = BM * BK3 * 4, WIDE3_B_BYTES = 256 * BK3 * 4;
-constexpr int WIDE3_STAGE_BYTES = 2 * WIDE3_A_BYTES + 2 * WIDE3_B_BYTES;
-constexpr size_t WIDE3_SMEM = size_t(WIDE3_STAGES) * WIDE3_STAGE_BYTES + 1024;
+constexpr int WIDE3_A_BYTES = BM * BK3 * 4;
 constexpr uint32_t kLayoutSw64 = 4;
+// BNT = 256 for layers with that many output channels; BNT = 128 is the same kernel for narrower layers whose
+// contraction is too long for the rotating accumulators of conv_igemm_kernel (see drained_kernel_needed).
+template <int BNT>
+struct Wide3Cfg {
+    static constexpr int B_BYTES = BNT * BK3 * 4;
+    static constexpr int STAGE_BYTES = 2 * WIDE3_A_BYTES + 2 * B_BYTES;   // 48 / 32 KiB
+    static constexpr int STAGES = BNT == 256 ? 4 : 6;
+    static constexpr size_t SMEM = size_t(STAGES) * STAGE_BYTES + 1024;
+    static constexpr int HALF = BNT / 2;   // columns folded by one epilogue thread
+};
 
+template <int BNT>
 __global__ void __launch_bounds__(320, 1)
 conv_igemm_wide3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_lo,
                         const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_b_lo,
                         const __grid_constant__ IgemmParams p, int m_tiles, int n_tiles) {
-    constexpr int BNT = 256, A_BYTES = WIDE3_A_BYTES, B_BYTES = WIDE3_B_BYTES, B_OFF = 2 * A_BYTES;
+    using Cfg = Wide3Cfg<BNT>;
+    constexpr int A_BYTES = WIDE3_A_BYTES, B_BYTES = Cfg::B_BYTES, B_OFF = 2 * A_BYTES;
+    constexpr int WIDE3_STAGES = Cfg::STAGES, WIDE3_STAGE_BYTES = Cfg::STAGE_BYTES, HALF = Cfg::HALF;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t full[WIDE3_STAGES], empty[WIDE3_STAGES], acc_full[2], acc_empty[2];
@@ -401,7 +411,7 @@ conv_igemm_wide3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         mbar_init_fence();
     }
     if (warp == 9) {
-        tmem_alloc(&tmem_slot, 512);
+        tmem_alloc(&tmem_slot, 2 * BNT);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -484,16 +494,16 @@ conv_igemm_wide3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         int q = 0;
         bool alive = true;
         for (int it = 0; it < my_tiles && alive; ++it) {
-            float run[128];
+            float run[HALF];
 #pragma unroll
-            for (int i = 0; i < 128; ++i) run[i] = 0.f;
+            for (int i = 0; i < HALF; ++i) run[i] = 0.f;
             for (int bi = 0; bi < batches; ++bi, ++q) {
                 const int b = q & 1;
                 if (!mbar_wait_warp(&acc_full[b], (q >> 1) & 1, p.status, 28)) { alive = false; break; }
                 tc_fence_after_sync();
-                const uint32_t acc = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(b) * BNT + uint32_t(half) * 128;
+                const uint32_t acc = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(b) * BNT + uint32_t(half) * HALF;
 #pragma unroll
-                for (int c0 = 0; c0 < 128; c0 += 32) {
+                for (int c0 = 0; c0 < HALF; c0 += 32) {
                     float t[32];
                     tmem_ld_32x32(acc + c0, t);
 #pragma unroll
@@ -504,7 +514,7 @@ conv_igemm_wide3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             }
             if (!alive) break;
             const int tile = blockIdx.x + it * gridDim.x;
-            const int mt = tile / n_tiles, n0 = (tile % n_tiles) * BNT + half * 128;
+            const int mt = tile / n_tiles, n0 = (tile % n_tiles) * BNT + half * HALF;
             const long long gb = 2ll * mt + (r >> 6);
             const int img = int(gb / blocks_per_img);
             const int rb = int(gb % blocks_per_img);
@@ -514,7 +524,7 @@ conv_igemm_wide3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 const int oy = p.out_sy * jy + p.out_oy, ox = p.out_sx * jx + p.out_ox;
                 float *dst_px = p.out + size_t(img) * p.out_c * plane + size_t(oy) * p.out_w + ox;
 #pragma unroll
-                for (int i = 0; i < 128; ++i) {
+                for (int i = 0; i < HALF; ++i) {
                     const int ch = n0 + i;
                     if (ch < p.out_c) {
                         float *dst = dst_px + size_t(ch) * plane;
@@ -526,7 +536,7 @@ conv_igemm_wide3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 9) tmem_dealloc(tmem_base, 512);
+    if (warp == 9) tmem_dealloc(tmem_base, 2 * BNT);
 }
 
 // ---- dW kernel ------------------------------------------------------------------------
@@ -1098,6 +1108,17 @@ struct Activation {
     int step;
 };
 
+// The tensor core's f32 accumulation loses about 3e-8 (relative) per accumulation step, and conv_igemm_kernel in
+// 3xTF32 makes 12 steps per 32-channel k-block into one of its 2 (128-wide tiles) or 4 (64- and 32-wide tiles)
+// rotating accumulators: 72 k-blocks (a 3x3 layer over 256 channels) measured 8.4e-6 against the 1e-5 bar with
+// two accumulators, 180 k-blocks 1.9e-5.  Beyond 300 steps per accumulator the layer goes to the kernel that
+// folds its accumulators into registers every 192 steps.
+bool drained_kernel_needed(size_t rows, const IgemmParams &p) {
+    const size_t kblocks = size_t(p.ntaps) * katsu_div_up((size_t)p.kc, (size_t)BK);
+    const size_t accumulators = rows <= 64 ? 4 : 2;
+    return katsu_div_up(kblocks, accumulators) * 12 > 300;
+}
+
 int32_t launch_igemm(katsu_cuda_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &ma_lo, const float *b_hi,
                      const float *b_lo, size_t taps, size_t rows, size_t inner, const IgemmParams &p, size_t total_blocks,
                      const Activation &act) {
@@ -1109,19 +1130,23 @@ int32_t launch_igemm(katsu_cuda_ctx *ctx, const CUtensorMap &ma, const CUtensorM
     }
     if (rows <= 32) return launch_igemm_bn<32, false>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
     if (rows <= 64) return launch_igemm_bn<64, false>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
-    if (wide_tiles_pay(rows)) {
+    const bool wide = wide_tiles_pay(rows);
+    if (!p.merge_x && (wide || drained_kernel_needed(rows, p))) {
+        const int bnt = wide ? 256 : 128;
         CUtensorMap mb, mb_lo, wa, wa_lo;
         const CUtensorMapSwizzle sw64 = CU_TENSOR_MAP_SWIZZLE_64B;
-        if (!taps_map(&mb, b_hi, taps, rows, inner, 256, BK3, sw64) || !taps_map(&mb_lo, b_lo, taps, rows, inner, 256, BK3, sw64) ||
+        if (!taps_map(&mb, b_hi, taps, rows, inner, bnt, BK3, sw64) || !taps_map(&mb_lo, b_lo, taps, rows, inner, bnt, BK3, sw64) ||
             !nhwc_map(&wa, act.hi, act.n, act.h, act.w, act.c, p.bw, p.bh, act.step, sw64, BK3) ||
             !nhwc_map(&wa_lo, act.lo, act.n, act.h, act.w, act.c, p.bw, p.bh, act.step, sw64, BK3))
             return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (wide conv operands)");
-        KATSU_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_wide3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WIDE3_SMEM));
-        const size_t m_tiles = katsu_div_up(total_blocks, 2), n_tiles = katsu_div_up(rows, (size_t)256);
+        auto kernel = wide ? conv_igemm_wide3_kernel<256> : conv_igemm_wide3_kernel<128>;
+        const size_t smem = wide ? Wide3Cfg<256>::SMEM : Wide3Cfg<128>::SMEM;
+        KATSU_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        const size_t m_tiles = katsu_div_up(total_blocks, 2), n_tiles = katsu_div_up(rows, (size_t)bnt);
         if (m_tiles * n_tiles > 0x7fffffffu / 64) return katsu_set_error(KATSU_ERR_UNSUPPORTED, "convolution too large for the tile counter");
         size_t grid = m_tiles * n_tiles;
         if (grid > (size_t)ctx->num_sms) grid = (size_t)ctx->num_sms;
-        KATSU_LAUNCH(ctx, conv_igemm_wide3_kernel, (unsigned)grid, 320, WIDE3_SMEM, wa, wa_lo, mb, mb_lo, p, (int)m_tiles, (int)n_tiles);
+        KATSU_LAUNCH(ctx, kernel, (unsigned)grid, 320, smem, wa, wa_lo, mb, mb_lo, p, (int)m_tiles, (int)n_tiles);
         return KATSU_OK;
     }
     return launch_igemm_bn<128, false>(ctx, ma, ma_lo, b_hi, b_lo, taps, rows, inner, p, total_blocks);
@@ -1257,7 +1282,19 @@ int32_t katsu_conv_igemm_dx(katsu_cuda_ctx *ctx, const float *w, const float *gr
     };
     // Stride 2, every class reached by some tap, tiles of at most 128 channels: one launch per ROW parity
     // computes both x-parity classes and writes them interleaved (IgemmParams::merge_x).
-    if (st == 2 && !some_class_empty && wd >= 2 && !wide_tiles_pay(c)) {
+    // (... unless a class's contraction is long enough to need the drained-accumulator kernel, which the
+    // per-class launches below can be routed to)
+    bool merged_ok = st == 2 && !some_class_empty && wd >= 2 && !wide_tiles_pay(c);
+    if (merged_ok && three) {
+        IgemmParams probe;
+        probe.kc = (int)k;
+        for (int py = 0; py < 2; ++py)
+            for (int px = 0; px < 2; ++px) {
+                probe.ntaps = class_taps(py, px, probe.off_y, probe.off_x, probe.b_tap);
+                merged_ok = merged_ok && !drained_kernel_needed(c, probe);
+            }
+    }
+    if (merged_ok) {
         for (int py = 0; py < 2 && py < (int)h; ++py) {
             IgemmParams p;
             p.out = dx;

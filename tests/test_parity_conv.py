@@ -43,6 +43,10 @@ SHAPES = [
     (1, 256, 9, 10, 256, 3, 3, 1, 1), (2, 64, 6, 7, 512, 3, 3, 2, 1), (1, 512, 8, 8, 272, 1, 1, 1, 0),
     # dW with 256-wide input-channel tiles whose second tile is a quarter full, half of an output-channel tile
     (2, 320, 6, 6, 64, 3, 3, 1, 1),
+    # contractions of 3 000 .. 5 800 terms with fewer than 256 output channels: forward (C x taps) and dX
+    # (K x taps) then take the kernel that folds its accumulators into registers every 192 accumulation steps
+    # (the rotating accumulators alone measured 1.1e-5 .. 1.9e-5 on these); the last one also has a stride
+    (2, 512, 10, 17, 132, 2, 3, 1, 1), (1, 132, 22, 11, 384, 5, 3, 1, 1), (4, 384, 19, 16, 128, 5, 3, 2, 1),
 ]
 
 
