@@ -1066,6 +1066,9 @@ DwPlan dw_plan(const katsu_cuda_ctx *ctx, const Shape &g) {
         const size_t blocks = out_tiles * cand, waves = katsu_div_up(blocks, (size_t)ctx->num_sms);
         if (blocks * 100 >= waves * ctx->num_sms * 95) { splits = cand; break; }
     }
+    // single-pass TF32 keeps a block's whole pixel range in tensor memory: at most 2048 k-blocks (65 536 pixels,
+    // ~4 000 accumulation steps per accumulator, ~1e-4 of accumulation loss against the 2e-3 bar of that mode)
+    if (!three && splits < katsu_div_up(total_groups, (size_t)2048)) splits = katsu_div_up(total_groups, (size_t)2048);
     if (splits > total_groups) splits = total_groups;
     if (splits < 1) splits = 1;
     plan.groups_per_split = katsu_div_up(total_groups, splits);
