@@ -105,3 +105,59 @@ def test_backward_beside_other_streams_is_bit_identical(oracle):
                 assert np.array_equal(context.download(pdw, w_count), dw_alone)
     finally:
         _close(lanes, extra)
+
+
+def test_pair_gemms_and_wide_convolutions_side_by_side(oracle):
+    """The kernels that run on pairs of thread blocks (large matmuls in both precision modes) and the wide
+    implicit-GEMM convolutions, one per stream, all at once: every stream's results equal what it produced
+    alone, bit for bit, and the matmul alone is held to the oracle."""
+    rng = np.random.default_rng(5)
+    m, k, n = 2100, 1024, 2332
+    a = rng.standard_normal(m * k).astype(np.float32)
+    b = rng.standard_normal(k * n).astype(np.float32)
+    conv = (2, 256, 28, 28, 256, 3, 3, 1, 1)
+    x = rng.standard_normal(conv[0] * conv[1] * conv[2] * conv[3]).astype(np.float32)
+    w = rng.standard_normal(conv[4] * conv[1] * 9).astype(np.float32)
+    y_count = conv[0] * conv[4] * conv[2] * conv[3]
+    plans = [(0, "gemm"), (1, "gemm"), (0, "conv"), (1, "conv")]
+    contexts = [cabi.Context(0) for _ in plans]
+    runs, reads, frees = [], [], []
+    for context, (mode, what) in zip(contexts, plans):
+        context.set_precision(mode)
+        if what == "gemm":
+            pa, pb, pc = context.upload(a), context.upload(b), context.alloc(m * n)
+            runs.append(lambda c=context, pa=pa, pb=pb, pc=pc: c.matmul_fwd(pa, pb, pc, m, k, n))
+            reads.append(lambda c=context, pc=pc: c.download(pc, m * n))
+            frees.append((pa, pb, pc))
+        else:
+            px, pw = context.upload(x), context.upload(w)
+            py, pdx, pdw = context.alloc(y_count), context.alloc(x.size), context.alloc(w.size)
+
+            def run(c=context, px=px, pw=pw, py=py, pdx=pdx, pdw=pdw):
+                c.conv2d_fwd(px, pw, py, *conv)
+                c.conv2d_bwd(px, pw, py, pdx, pdw, *conv, 0)
+
+            runs.append(run)
+            reads.append(lambda c=context, py=py, pdx=pdx, pdw=pdw: np.concatenate(
+                [c.download(py, y_count), c.download(pdx, x.size), c.download(pdw, w.size)]))
+            frees.append((px, pw, py, pdx, pdw))
+    try:
+        alone = []
+        for context, run, read in zip(contexts, runs, reads):
+            run()
+            context.sync()
+            alone.append(read())
+        assert_parity(alone[0], oracle.matmul_f64(a, b, m, k, n), k, what="3xTF32 matmul alone")
+        for _ in range(REPEATS):
+            for _ in range(3):
+                for run in runs:
+                    run()
+            for context in contexts:
+                context.sync()
+            for i, read in enumerate(reads):
+                assert np.array_equal(read(), alone[i]), ("stream", i, plans[i])
+    finally:
+        for context, pointers in zip(contexts, frees):
+            for p in pointers:
+                context.free(p)
+            context.close()
