@@ -282,7 +282,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 {
                     // pixel pair (oy, 2 jx), (oy, 2 jx + 1): class 0 is held, class 1 completes the pair
                     const bool ok2 = pixel_ok && jx < p.grid_w2;
-                    const bool vec = ok2 && ((p.out_w & 1) == 0) && !p.accumulate;
+                    // (pairs start at even x: 8-byte aligned when the rows and the tensor itself are)
+                    const bool vec = ok2 && ((p.out_w & 1) == 0) && !p.accumulate && (reinterpret_cast<uintptr_t>(p.out) & 7u) == 0;
 #pragma unroll
                     for (int c0 = 0; c0 < BNT; c0 += 32) {
                         float v[32];

@@ -72,7 +72,8 @@ stencil_fwd_kernel(const float *__restrict__ x, const float *__restrict__ w, flo
 
     const int oy = y0 + ty, ox = x0 + 4 * tx;
     const bool row_ok = oy < d.h;
-    const bool vec_ok = (d.w % 4 == 0) && (ox + 3 < d.w);
+    // 128-bit stores need rows that start on 16 bytes: W a multiple of 4 and the tensor itself aligned
+    const bool vec_ok = (d.w % 4 == 0) && (ox + 3 < d.w) && (reinterpret_cast<uintptr_t>(y) & 15u) == 0;
     const size_t plane = size_t(d.h) * d.w;
     float *yrow = y + size_t(n) * d.k * plane + size_t(oy) * d.w + ox;
 
@@ -202,7 +203,7 @@ stencil_dx_kernel(const float *__restrict__ w, const float *__restrict__ g, floa
     }
 
     const int ix = x0 + 4 * tx;
-    const bool vec_ok = (d.w % 4 == 0) && (ix + 3 < d.w);
+    const bool vec_ok = (d.w % 4 == 0) && (ix + 3 < d.w) && (reinterpret_cast<uintptr_t>(dx) & 15u) == 0;
 #pragma unroll
     for (int c = 0; c < CIN; ++c)
 #pragma unroll
@@ -251,7 +252,7 @@ stencil_dw_kernel(const float *__restrict__ x, const float *__restrict__ g, floa
     const int tiles_per_image = d.tiles_x * d.tiles_y;
     const int total_tiles = d.n * tiles_per_image;
     const size_t plane = size_t(d.h) * d.w;
-    const bool w_vec = (d.w % 4 == 0);
+    const bool w_vec = (d.w % 4 == 0) && (reinterpret_cast<uintptr_t>(g) & 15u) == 0;
 
     for (int grp = 0; grp < groups; ++grp) {
         float acc0[TAPS], acc1[TAPS];
