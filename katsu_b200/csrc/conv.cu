@@ -147,6 +147,8 @@ extern "C" int32_t katsu_cuda_conv2d_stage(katsu_cuda_ctx *ctx, const float *x, 
     KATSU_TRY(katsu_bind(ctx));
     KATSU_REQUIRE(x != nullptr && staged != nullptr, "null tensor");
     KATSU_REQUIRE(n > 0 && c > 0 && h > 0 && wd > 0, "empty input");
+    // inputs for which katsu_cuda_conv2d_staged_floats reports 0 whatever the filter: nothing to write
+    if (ctx->precision == KATSU_MODE_FP32 || c < 16 || (c & 3) != 0) return KATSU_OK;
     return katsu_conv_igemm_stage(ctx, x, staged, n, c, h, wd);
 }
 
