@@ -717,9 +717,10 @@ int32_t katsu_umma_gemm_wide(katsu_cuda_ctx *ctx, const float *a, const float *b
     }
     if (ctx->precision != KATSU_MODE_TF32) return KATSU_OK;
     if (M < 128 || N < 256 || K < 32) return KATSU_OK;
-    // the whole contraction accumulates in tensor memory: ~3e-8 lost per step of 8, so 2^18 columns cost about
-    // 1e-3 of the mode's 2e-3 bar; longer ones go to the kernel that drains every 32 k-blocks
-    if (K > (size_t(1) << 18)) return KATSU_OK;
+    // the whole contraction accumulates in tensor memory, which loses ~3e-8 per accumulation step: measured
+    // 1.17e-3 at K = 200 000 against 7.7e-4 for the kernel that drains every 32 k-blocks (bar of this mode:
+    // 2e-3).  Up to 2^16 columns the loss stays a small part of the mode's own rounding; longer ones go there.
+    if (K > (size_t(1) << 16)) return KATSU_OK;
     const size_t tiles = katsu_div_up(M, (size_t)BM) * katsu_div_up(N, (size_t)BN);
     if (tiles * 2 < (size_t)ctx->num_sms || tiles > 0x3fffffffu) return KATSU_OK;
     if (katsu_div_up(K, (size_t)BK) * tiles > 0x7fffffffu) return KATSU_OK;  // the ring counter is an int
