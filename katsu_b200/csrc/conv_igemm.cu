@@ -553,6 +553,10 @@ struct DwParams {
     int stride;
     int three_pass;
     int grouped;                // 1: the maps are 5-D (channel groups as a dimension), one load per operand tile
+    // Single-pass TF32 on layers of at most 128 input channels: a block's 256 accumulator columns hold
+    // taps_per_block filter taps side by side (cpad = 256 / taps_per_block columns each), all fed by the same g
+    // tile, so that tile is fetched and read once per 2 or 4 taps instead of once per tap.
+    int taps_per_block, cpad;
     int *status;
     short off_y[MAX_TAPS], off_x[MAX_TAPS];
 };
@@ -589,9 +593,11 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
     __shared__ uint64_t full[STAGES_D], empty[STAGES_D], drained, batch_done;
     __shared__ uint32_t tmem_slot;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ctiles = (p.c + BNT - 1) / BNT;
+    const int tpb = (SINGLE && BNT == 256) ? p.taps_per_block : 1;   // > 1: one channel tile, several taps
+    const int ctiles = tpb > 1 ? 1 : (p.c + BNT - 1) / BNT;
     const int c0 = (blockIdx.x % ctiles) * BNT, k0 = (blockIdx.x / ctiles) * BM;
-    const int tap = blockIdx.y;
+    const int tap = blockIdx.y * tpb;
+    const int taps_here = (p.taps - tap) < tpb ? (p.taps - tap) : tpb;
     const int groups_per_img = p.groups_x * p.groups_y;
     const long long total_groups = (long long)p.n_img * groups_per_img;
     const long long g_begin = (long long)blockIdx.z * p.groups_per_split;
@@ -624,7 +630,7 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
         for (int i = 0; i < kblocks; ++i) {
             const int s = i % STAGES_D;
             if (i >= STAGES_D && !mbar_wait(&empty[s], ((i / STAGES_D) - 1) & 1, p.status, 31)) break;
-            mbar_arrive_expect_tx(&full[s], PARTS * (TILE_BYTES + BNT * BK * 4));
+            mbar_arrive_expect_tx(&full[s], tpb > 1 ? TILE_BYTES + taps_here * p.cpad * BK * 4 : PARTS * (TILE_BYTES + BNT * BK * 4));
             unsigned char *st = smem + s * stage_bytes;
             const long long gidx = g_begin + i;
             const int img = int(gidx / groups_per_img);
@@ -633,6 +639,14 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
             for (int part = 0; part < PARTS; ++part) {
                 const CUtensorMap *mg = part ? &map_g_lo : &map_g;
                 const CUtensorMap *mx = part ? &map_x_lo : &map_x;
+                if (tpb > 1) {
+                    // (only reached with grouped maps and one part) the g tile once, one x tile per tap
+                    tma_load_5d(st, mg, &full[s], 0, ox0, oy0, k0 / 32, img);
+                    for (int tt = 0; tt < taps_here; ++tt)
+                        tma_load_5d(st + Cfg::B_OFF + tt * p.cpad * BK * 4, mx, &full[s], 0,
+                                    ox0 * p.stride + p.off_x[tap + tt], oy0 * p.stride + p.off_y[tap + tt], 0, img);
+                    continue;
+                }
                 if (p.grouped) {
                     // one instruction per operand tile: the TMA unit's per-instruction cost, not its
                     // bandwidth, bounds a stage made of twelve 4 KiB boxes
@@ -698,8 +712,12 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
         const bool alive = kblocks == 0 || mbar_wait(&batch_done, 0, p.status, 34);
         tc_fence_after_sync();
         const int used_acc = kblocks < NACC_D ? kblocks : NACC_D;
-        float *dst = p.partial + ((size_t(blockIdx.z) * p.taps + tap) * p.k + (oc < p.k ? oc : 0)) * p.c;
         for (int q = 0; q < BNT / 32; ++q) {
+            // columns q * 32 .. + 31: of tap `tap + tt`, channels ch0 .. (one tap and c0 + q * 32 without tap packing)
+            const int tt = tpb > 1 ? (q * 32) / p.cpad : 0;
+            const int ch0 = tpb > 1 ? (q * 32) % p.cpad : c0 + q * 32;
+            if (tt >= taps_here) break;
+            float *dst = p.partial + ((size_t(blockIdx.z) * p.taps + tap + tt) * p.k + (oc < p.k ? oc : 0)) * p.c;
             float v[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0.f;
@@ -712,7 +730,7 @@ conv_dw_igemm_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_con
             if (oc < p.k) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
-                    if (c0 + q * 32 + i < p.c) dst[c0 + q * 32 + i] = v[i];
+                    if (ch0 + i < p.c) dst[ch0 + i] = v[i];
             }
         }
       }
@@ -1040,6 +1058,7 @@ bool igemm_shape(const katsu_cuda_ctx *ctx, const Shape &g) {
 // Split of the dW contraction over pixel groups and the scratch it needs.
 struct DwPlan {
     size_t bnt, splits, groups_per_split, partial_floats, scratch_floats;
+    size_t taps_per_block;  // > 1: single-pass TF32 with several taps side by side in a 256-column tile
     bool all_taps;  // narrow layer: conv_dw_taps_kernel, `splits` counts its chunks
 };
 
@@ -1050,6 +1069,11 @@ DwPlan dw_plan(const katsu_cuda_ctx *ctx, const Shape &g) {
     // channel-tile width of the c side: narrow layers get narrow MMAs and operand tiles
     const bool three = ctx->precision == KATSU_MODE_3XTF32;
     plan.bnt = g.c <= 32 ? 32 : g.c <= 64 ? 64 : (!three && g.c >= 256 && g.c % 32 == 0 && g.k % 32 == 0) ? 256 : 128;
+    plan.taps_per_block = 1;
+    if (!three && g.c > 32 && g.c <= 128 && g.c % 32 == 0 && g.k % 32 == 0 && taps > 1) {
+        plan.taps_per_block = g.c <= 64 ? 4 : 2;
+        plan.bnt = 256;
+    }
     // two stages of (g hi/lo 32 KiB + x hi/lo 8 KiB per tap) must fit in shared memory: taps <= 10
     plan.all_taps = g.c <= 32 && g.k <= (size_t)BM && taps <= 10 && total_groups <= 0x7fffffffu;
     if (plan.all_taps) {
@@ -1059,7 +1083,9 @@ DwPlan dw_plan(const katsu_cuda_ctx *ctx, const Shape &g) {
         plan.scratch_floats = (padded(g.n * g.c * g.h * g.w) + padded(g.n * g.k * g.oh * g.ow)) * (three ? 2 : 1) + padded(plan.partial_floats);
         return plan;
     }
-    const size_t out_tiles = katsu_div_up(g.k, (size_t)BM) * katsu_div_up(g.c, plan.bnt) * taps;
+    const size_t out_tiles = plan.taps_per_block > 1
+                                 ? katsu_div_up(g.k, (size_t)BM) * katsu_div_up(taps, plan.taps_per_block)
+                                 : katsu_div_up(g.k, (size_t)BM) * katsu_div_up(g.c, plan.bnt) * taps;
     // Split the pixel range so that the grid fills whole waves of the GPU: the smallest split
     // count (at least two blocks' worth of work per SM) whose last wave is >= 95 % full.
     size_t splits = katsu_div_up(size_t(ctx->num_sms) * 2, out_tiles);
@@ -1381,6 +1407,8 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr
     }
     const DwPlan plan = dw_plan(ctx, g);
     const size_t bnt = plan.bnt, splits = plan.splits;
+    p.taps_per_block = (int)plan.taps_per_block;
+    p.cpad = 256 / (int)plan.taps_per_block;
     p.groups_per_split = (int)plan.groups_per_split;
     float *base = nullptr;
     KATSU_TRY(katsu_scratch(ctx, plan.scratch_floats, &base));
@@ -1416,8 +1444,9 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr
         CUtensorMap ng, ng_lo, nx, nx_lo;
         const bool grouped = nhwc_grouped_map(&ng, gt, n, oh, ow, k, 8, 4, 1, BM / 32, via_gemm ? CU_TENSOR_MAP_SWIZZLE_NONE : sw) &&
                              nhwc_grouped_map(&ng_lo, three ? gt_lo : gt, n, oh, ow, k, 8, 4, 1, BM / 32, sw) &&
-                             nhwc_grouped_map(&nx, xt, n, h, wd, c, 8, 4, (int)stride, (int)bnt / 32, sw) &&
-                             nhwc_grouped_map(&nx_lo, three ? xt_lo : xt, n, h, wd, c, 8, 4, (int)stride, (int)bnt / 32, sw);
+                             nhwc_grouped_map(&nx, xt, n, h, wd, c, 8, 4, (int)stride, (plan.taps_per_block > 1 ? p.cpad : (int)bnt) / 32, sw) &&
+                             nhwc_grouped_map(&nx_lo, three ? xt_lo : xt, n, h, wd, c, 8, 4, (int)stride, (plan.taps_per_block > 1 ? p.cpad : (int)bnt) / 32, sw);
+        if (!grouped && plan.taps_per_block > 1) return katsu_set_error(KATSU_ERR_CUDA, "cuTensorMapEncodeTiled failed (conv dW, grouped)");
         if (grouped) { mg = ng; mg_lo = ng_lo; mx = nx; mx_lo = nx_lo; p.grouped = 1; }
     }
     if (via_gemm) {
@@ -1451,7 +1480,8 @@ int32_t katsu_conv_igemm_dw(katsu_cuda_ctx *ctx, const float *x, const float *gr
         size_t grid = splits < (size_t)ctx->num_sms ? splits : (size_t)ctx->num_sms;
         KATSU_LAUNCH(ctx, conv_dw_taps_kernel, (unsigned)grid, 192, smem, mg, mg_lo, mx, mx_lo, q);
     } else {
-        dim3 grid((unsigned)(katsu_div_up(k, (size_t)BM) * katsu_div_up(c, bnt)), (unsigned)taps, (unsigned)splits);
+        dim3 grid((unsigned)(katsu_div_up(k, (size_t)BM) * (plan.taps_per_block > 1 ? 1 : katsu_div_up(c, bnt))),
+                  (unsigned)katsu_div_up(taps, plan.taps_per_block), (unsigned)splits);
         if (three) {
             auto kernel = bnt == 32 ? conv_dw_igemm_kernel<32, false> : bnt == 64 ? conv_dw_igemm_kernel<64, false>
                                                                                   : conv_dw_igemm_kernel<128, false>;
