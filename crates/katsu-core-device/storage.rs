@@ -69,6 +69,10 @@ impl From<katsu_cuda::CudaError> for TensorError {
 //
 //   conv2d.rs:99-103    Conv2D::forward, after Geometry::new:
 //       katsu_cuda::conv2d_forward(ctx, x.device()?, w.device()?, None, false, &mut y, &geometry.into())?
+//       wide layers (katsu_cuda::conv2d_staged_len(ctx, &g)? > 0): the input node keeps a second device buffer
+//       beside `device`, `staged: OnceCell<(Precision, DeviceBuf)>`, written by katsu_cuda::conv2d_stage on the
+//       first use in the current precision mode; forward and backward then call conv2d_forward_staged /
+//       conv2d_backward_staged with it (one staging pass per step instead of two; values never change)
 //   conv2d.rs:283-290   backward_buffers:
 //       katsu_cuda::conv2d_backward(ctx, x, w, g, None, Some(&mut dx), Some(&mut dw), &geometry.into(), false)?
 //   tensor.rs:374-391   Op::backward, Conv2D arm: the same call with the pending adjoints of the two
