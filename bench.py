@@ -616,7 +616,7 @@ def stem_leg(job, args):
         barrier()
     copy_min = job.reduce_over_ranks([copy_gbs["h2d"], copy_gbs["d2h"]], "min")
 
-    def e2e_step(slot, fused=True):
+    def e2e_step(slot, fused=True, read_dx=True):
         par = slot & 1
         # a lane must not overwrite a dW partial that lane 0 has not yet added (two steps back)
         for lane_ctx in lanes[1:]:
@@ -636,7 +636,8 @@ def stem_leg(job, args):
                 lane_ctx.call("katsu_cuda_add", b["y"], b["y"], b["g"], cnt * per_img_y)
                 lane_ctx.conv2d_bwd(b["x"], b["w"], b["g"], b["dx"], 0, *cg, 0)
                 lane_ctx.conv2d_bwd(b["x"], b["w"], b["g"], 0, b["dw"][par], *cg, 1 if i >= n_lanes else 0)
-            lane_ctx.d2h_async(dx_pin[first_img * per_img_x:(first_img + cnt) * per_img_x], b["dx"])
+            if read_dx:
+                lane_ctx.d2h_async(dx_pin[first_img * per_img_x:(first_img + cnt) * per_img_x], b["dx"])
         total = lane_buf[0]["dw"][par]
         for j in range(1, min(n_lanes, n_chunks)):
             lanes[j].record(lane_done[j])
@@ -653,14 +654,14 @@ def stem_leg(job, args):
 
     lead.record(combined[0]), lead.record(combined[1])
 
-    def e2e_run(fused):
-        e2e_step(e2e_steps, fused)
+    def e2e_run(fused, read_dx=True):
+        e2e_step(e2e_steps, fused, read_dx)
         for lane_ctx in lanes:
             lane_ctx.sync()
         barrier()
         t0 = time.perf_counter()
         for step_index in range(e2e_steps):
-            e2e_step(step_index, fused)
+            e2e_step(step_index, fused, read_dx)
         for lane_ctx in lanes:
             lane_ctx.sync()
         ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
@@ -668,6 +669,9 @@ def stem_leg(job, args):
         return ms
 
     e2e_unfused_ms = e2e_run(False)  # the gradient 2y written out by a separate pass, for comparison
+    # dX computed but left on the device (what a training loop that only needs dW and the loss pays: the
+    # host classes download a gradient when it is read); a second figure, the headline below reads dX back
+    e2e_dw_only_ms = e2e_run(True, read_dx=False)
     e2e_ms = e2e_run(True)
     # Every step's dW reached the host; the inputs are the same every step, so the steps should
     # agree bit for bit.  The largest deviation from step 0 (relative to max |dW|) is reported as
@@ -679,8 +683,8 @@ def stem_leg(job, args):
     dw_differing = sum(1 for i in range(1, e2e_steps) if not np.array_equal(dw_pin[0], dw_pin[i]))
 
     step_min, e2e_min = job.reduce_over_ranks([ms_per_step, e2e_ms], "min")
-    stats = [ms_per_step, e2e_ms, host_enqueue_ms, allreduce_ms or 0.0, e2e_unfused_ms]
-    ms_per_step, e2e_ms, host_enqueue_max, allreduce_max, e2e_unfused_ms = job.reduce_over_ranks(stats, "max")
+    stats = [ms_per_step, e2e_ms, host_enqueue_ms, allreduce_ms or 0.0, e2e_unfused_ms, e2e_dw_only_ms]
+    ms_per_step, e2e_ms, host_enqueue_max, allreduce_max, e2e_unfused_ms, e2e_dw_only_ms = job.reduce_over_ranks(stats, "max")
 
     line = None
     if rank == 0:
@@ -723,6 +727,9 @@ def stem_leg(job, args):
                     "pipeline": f"{n_chunks} batch chunks over {n_lanes} streams, pinned host buffers, one host sync after the last step",
                     "upstream_gradient": "2y read from y by the backward kernels (scaled outputs)",
                     "ms_per_step_with_gradient_written_out": e2e_unfused_ms,
+                    "leaving_dx_on_the_device": {"ms_per_step": e2e_dw_only_ms,
+                                                 "images_per_s": global_batch / (e2e_dw_only_ms * 1e-3),
+                                                 "d2h_bytes_per_step": 4 * w_count},
                     "copy_only_gbs_min_over_ranks": {"h2d": copy_min[0], "d2h": copy_min[1],
                                                      "note": "one direction at a time, all ranks at once"},
                     "host_affinity": affinity,
