@@ -19,8 +19,12 @@
 //             one launch per stride-parity class of input pixels      (A, B K-major)
 //   dW      : dW[tap][oc, c] = sum_pixel G[pixel, oc] * X[pixel*s + tap - p, c] (A, B MN-major)
 //
-// Tiles are 128 (two 64-pixel blocks, or 128 output channels for dW) x 128, k-blocks of
-// 32, 3-stage TMA pipeline, four rotating TMEM accumulators (see umma_gemm.cu for why).
+// Tiles are 128 (two 64-pixel blocks, or 128 output channels for dW) x 32..256 by channel count, k-blocks of
+// 32 channels or pixels, both operands read by the tensor core from shared memory.  In 3xTF32 the stages carry
+// hi and lo halves and accumulation chains are kept short (rotating accumulators; beyond ~300 accumulation steps,
+// or with 256-wide tiles, two accumulators that are folded into registers in turn); in single-pass TF32 the
+// stages carry hi only, the ring is deeper and tiles are as wide as the layer allows (256 channels, or several
+// filter taps side by side in dW), because that mode is bound by getting operands into shared memory.
 #include "common.cuh"
 #include "sm100.cuh"
 
